@@ -386,6 +386,90 @@ int32_t sllm_engine_step_launches(const sllm_engine* e);
 /* total launches issued by this engine since creation */
 int64_t sllm_engine_total_launches(const sllm_engine* e);
 
+/* ------------------------------------------------------------------------------------------------------
+ * Ragged token batches (sllm_seq_*): building blocks for models that mix softmax attention over a paged cache with
+ * recurrent layers (additive: the reference has one Llama forward, source/model/model.cpp:40-140). A step brings T tokens
+ * that belong to nseg segments; a segment is a run of consecutive positions of ONE sequence (a portion of a prompt, or
+ * one decoded token) and its tokens are adjacent in the batch. Activations are fp32 [T][ld]; every matrix argument
+ * comes with its row stride so that the columns of one wide projection can feed several consumers. Weights are fp32 or
+ * bf16 (SLLM_F32 / SLLM_BF16). Per-sequence state (recurrent state, convolution tail) lives in slot-indexed fp32 arrays
+ * owned by the caller; the softmax attention's keys and values live in page pools [pages][kv_heads][page_len][width]
+ * (fp32 or bf16) addressed through a block table. All launchers enqueue on `stream`, allocate nothing and do not synchronise.
+ * ---------------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t T, nseg;             /* tokens and segments of this step */
+    const int32_t* tok_slot;     /* [T]    state slot (= row of the block table) of each token's sequence */
+    const int32_t* tok_pos;      /* [T]    position of each token in its sequence */
+    const int32_t* seg_start;    /* [nseg] first token of the segment in the batch */
+    const int32_t* seg_len;      /* [nseg] */
+    const int32_t* seg_slot;     /* [nseg] */
+    const int32_t* seg_pos0;     /* [nseg] position of the segment's first token */
+    const int32_t* block_table;  /* [slots][max_pages] page of positions i*page_len.., -1 = none */
+    int32_t max_pages, page_len; /* page_len: a multiple of 32 */
+    int32_t n_qtiles;            /* attention work list: tiles of up to 32 consecutive queries of one segment */
+    const int32_t* qt_seg;       /* [n_qtiles] segment of the tile */
+    const int32_t* qt_off;       /* [n_qtiles] offset of its first query inside the segment */
+} sllm_seq_batch;
+
+/* out[s][t][:] = table[ids[t]][:] for every stream s (a model with one residual stream passes streams = 1) */
+int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32_t vocab, int32_t d, int32_t streams, float* out,
+                   int32_t T, sllm_stream_t stream);
+/* u = sum_s coef[s] * x[s] (coef NULL = all ones), then, if norm_w is given, the RMS norm in `groups` equal consecutive parts:
+ * every part divided by sqrt(mean(part^2) + eps), the whole multiplied by norm_w. x: [streams][T][d], y: [T][d]. */
+int sllm_seq_hyper_read(const float* x, int32_t streams, int32_t T, int32_t d, const float* coef, const float* norm_w, int32_t groups,
+                        float eps, float* y, sllm_stream_t stream);
+/* all streams at once from the old ones: x[t] <- sum_s mix[s][t] * x[s] + outc[t] * y (mix NULL = identity, outc NULL = ones) */
+int sllm_seq_hyper_write(float* x, int32_t streams, int32_t T, int32_t d, const float* mix, const float* outc, const float* y,
+                         sllm_stream_t stream);
+/* C[b] = alpha * (A[b] . W[b]^T + bias[b]) (+ C[b] if accumulate): A fp32 [T][lda] (rounded to bf16 on load if round_a), W [N][ldw]
+ * row-major in w_dtype, bias fp32 [N] or NULL, C fp32 [T][ldc]; `batch` independent products whose operands lie *_bs elements apart
+ * (block-diagonal matrices). Any T, N, K. With a16 (scratch of T*K bf16 values) given, bf16 weights and a shape its tiles take, the
+ * product runs on the tensor cores (tcgen05); otherwise on fp32 FMAs. */
+int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc,
+                    int32_t T, int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs,
+                    int64_t w_bs, int64_t bias_bs, int64_t c_bs, void* a16, sllm_stream_t stream);
+/* PolyNorm: out = c0*N(z) + c1*N(z^2) + c2*N(z^3) + c3, powers element-wise, N(v) = v / sqrt(mean(v^2) + eps) over a row; coef: 4 floats */
+int sllm_seq_polynorm(const float* z, int32_t ldz, const float* coef, float eps, float* out, int32_t ldo, int32_t T, int32_t n,
+                      sllm_stream_t stream);
+/* out[i][:] = x[rows[i]][:] (n rows of d floats) */
+int sllm_seq_gather_rows(const float* x, int32_t ldx, const int32_t* rows, int32_t n, int32_t d, float* out, sllm_stream_t stream);
+/* Rotary positions on q (in place) and k, rotated values, and the cache write: the first 2*n_freq dimensions of every q / k head turn
+ * by pos * freq[i] with cos and sin multiplied by `magnitude`; every value head turns over all its dv dimensions by pos * vfreq[m]
+ * (vfreq NULL = values are stored as they are); freq and vfreq are DOUBLE arrays and the angle is formed in double, so that its error does not
+ * grow with the position. layout 0 pairs dimension 2i with 2i+1, layout 1 pairs i with i + half. k and v go to
+ * their pools at (page of pos, kv head, pos % page_len). */
+int sllm_seq_rotary_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk,
+                       int32_t kv_heads, const float* v, int32_t ldv, int32_t dv, const double* freq, int32_t n_freq, float magnitude,
+                       const double* vfreq, int32_t layout, void* k_pool, void* v_pool, int32_t kv_dtype, sllm_stream_t stream);
+/* Causal softmax attention of every token over positions 0..pos of its own sequence: score = (q . k) * scale, query head h reads
+ * key/value head h / (heads / kv_heads). Keys are visited in tiles of 32, cut into nsplit interleaved shares; the partial results
+ * (running maximum, sum, unnormalised output) go to ws: [T][heads][nsplit][dv + 2] floats. */
+int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t kv_heads, int32_t dk, int32_t dv,
+                       float scale, const void* k_pool, const void* v_pool, int32_t kv_dtype, int32_t nsplit, float* ws,
+                       sllm_stream_t stream);
+/* Merges the shares, normalises, turns every head's output back by -pos * vfreq[m] (vfreq NULL = not), multiplies head h by
+ * sigmoid(gate[t][h]) (gate NULL = not) and stores out[t][h*dv ..]. */
+int sllm_seq_attention_finish(const sllm_seq_batch* b, const float* ws, int32_t nsplit, int32_t heads, int32_t dv, const double* vfreq,
+                              int32_t layout, const float* gate, int32_t ldg, float* out, int32_t ldo, sllm_stream_t stream);
+/* Causal convolution per channel over each sequence: u[t][c] = cb[c] + sum_k w[c][k] * x[t - (taps-1-k)][c]; inputs before the segment
+ * come from tail[slot][taps-1][channels] (zeros for a new sequence). The tail is NOT updated here (sllm_seq_rglru_scan does it). */
+int sllm_seq_conv(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* cb,
+                  const float* tail, float* u, int32_t ldu, sllm_stream_t stream);
+/* Real-gated linear recurrent unit: r = sigmoid(lr), i = sigmoid(li), log a = -c * r * softplus(lam), S <- a*S + sqrt(1 - a^2) * i * u,
+ * out = S * gelu_tanh(ypre). state: [slots][channels] fp32, read and written. Also moves the convolution tail on: tail[slot] <- the
+ * last taps-1 rows of (tail[slot] ++ xconv rows of the segment) (xconv NULL = no tail). */
+int sllm_seq_rglru_scan(const sllm_seq_batch* b, const float* u, int32_t ldu, const float* lr, const float* li, int32_t ldg,
+                        const float* ypre, int32_t ldy, const float* lam, float c, int32_t channels, float* state, const float* xconv,
+                        int32_t ldx, int32_t taps, float* tail, float* out, int32_t ldo, sllm_stream_t stream);
+/* Gated linear attention, token by token per head: alpha = sigmoid(z)^(1/tau) per key channel, S <- diag(alpha) S + k v^T (S: dk x dv),
+ * o = S^T (q * qscale). state: [slots][heads][dk][dv] fp32, read and written. */
+int sllm_seq_gla_scan(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv,
+                      const float* z, int32_t ldz, int32_t heads, int32_t dk, int32_t dv, float qscale, float tau, float* state, float* o,
+                      int32_t ldo, sllm_stream_t stream);
+/* out[t][h*dv + j] = o[t][h*dv + j] / sqrt(mean_j(o^2) + eps) * w[j] * silu(g[t][h*dv + j]) */
+int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t ldg, const float* w, int32_t heads, int32_t dv, float eps,
+                           float* out, int32_t ldout, int32_t T, sllm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

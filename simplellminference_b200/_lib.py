@@ -116,7 +116,72 @@ SIGNATURES = {
     "sllm_engine_total_launches": (_L, [_P]),
 }
 
+
+class SeqBatch(C.Structure):
+    """sllm_seq_batch: one step's ragged token batch (device pointers to its index arrays)."""
+    _fields_ = [("T", _I), ("nseg", _I), ("tok_slot", _P), ("tok_pos", _P), ("seg_start", _P), ("seg_len", _P), ("seg_slot", _P),
+                ("seg_pos0", _P), ("block_table", _P), ("max_pages", _I), ("page_len", _I), ("n_qtiles", _I), ("qt_seg", _P), ("qt_off", _P)]
+
+
+_B = C.POINTER(SeqBatch)
+SIGNATURES.update({
+    "sllm_seq_embed": (C.c_int, [_P, _P, _I, _I, _I, _I, _P, _I, _P]),
+    "sllm_seq_hyper_read": (C.c_int, [_P, _I, _I, _I, _P, _P, _I, _F, _P, _P]),
+    "sllm_seq_hyper_write": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "sllm_seq_linear": (C.c_int, [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _L, _L, _L, _L, _P, _P]),
+    "sllm_seq_polynorm": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
+    "sllm_seq_gather_rows": (C.c_int, [_P, _I, _P, _I, _I, _P, _P]),
+    "sllm_seq_rotary_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _F, _P, _I, _P, _P, _I, _P]),
+    "sllm_seq_attention": (C.c_int, [_B, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _P, _P]),
+    "sllm_seq_attention_finish": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _P, _I, _P, _I, _P]),
+    "sllm_seq_conv": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
+    "sllm_seq_rglru_scan": (C.c_int, [_B, _P, _I, _P, _P, _I, _P, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _I, _P]),
+    "sllm_seq_gla_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P]),
+    "sllm_seq_headnorm_gate": (C.c_int, [_P, _I, _P, _I, _P, _I, _I, _F, _P, _I, _I, _P]),
+})
+
+# The ragged-token-batch part of the library can be built and loaded on its own (`make -C csrc seq` -> libsllm_b200_seq.so: the
+# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs seven
+# translation units compiled, not all of them. The full library contains the same objects and is preferred when it exists.
+SEQ_LIB_PATH = os.path.join(HERE, "lib", "libsllm_b200_seq.so")
+SEQ_SYMBOL_PREFIXES = ("sllm_seq_", "sllm_kvpages_", "sllm_sample_", "sllm_last_error", "sllm_abi_version", "sllm_tune", "sllm_device_info",
+                       "sllm_prefill_gemm_")
+
 _lib = None
+_seq_lib = None
+
+
+def build_seq() -> None:
+    """Compile the ragged-token-batch part of the library in-tree (nvcc, sm_100a)."""
+    import subprocess
+    subprocess.run(["make", "-s", "-j8", "-C", os.path.join(HERE, "csrc"), "seq"], check=True)
+
+
+def load_seq(build: bool = False) -> C.CDLL:
+    """The library for the sllm_seq_* blocks: the full one if it is built, else the part that holds them (built first if ``build``)."""
+    global _seq_lib
+    if _seq_lib is None:
+        if _lib is not None or os.path.exists(LIB_PATH):
+            _seq_lib = load()
+        else:
+            if not os.path.exists(SEQ_LIB_PATH):
+                if not build:
+                    raise FileNotFoundError(f"neither {LIB_PATH} nor {SEQ_LIB_PATH} is built; simplellminference_b200 has no CPU or PyTorch fallback")
+                build_seq()
+            import torch  # noqa: F401  (libcudart of the process first)
+            lib = C.CDLL(SEQ_LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                if name.startswith(SEQ_SYMBOL_PREFIXES):
+                    fn = getattr(lib, name)
+                    fn.restype = res
+                    fn.argtypes = args
+            _seq_lib = lib
+    return _seq_lib
+
+
+def check_seq(rc: int) -> None:
+    if rc != 0:
+        raise SllmError(rc, load_seq().sllm_last_error().decode(errors="replace"))
 
 
 def load() -> C.CDLL:

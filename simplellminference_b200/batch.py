@@ -17,7 +17,7 @@ class KvPages:
     """Host bookkeeping of the paged cache (free stack + per-sequence page lists); no device involved."""
 
     def __init__(self, n_pages: int, page_len: int, max_seqs: int, max_pages_per_seq: int):
-        self.lib = _lib.load()
+        self.lib = _lib.load_seq()   # the full library, or the part of it that carries the bookkeeping
         self.h = self.lib.sllm_kvpages_create(n_pages, page_len, max_seqs, max_pages_per_seq)
         if not self.h:
             raise _lib.SllmError(_lib.EINVAL, self.lib.sllm_last_error().decode(errors="replace"))

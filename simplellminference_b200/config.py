@@ -57,3 +57,116 @@ PRESETS = {
     "tiny_gqa": ModelShape(512, 32, 128, 64, 384, 48, 3, 4, 2),
     "tiny_mha_hd48": ModelShape(300, 48, 96, 96, 200, 40, 2, 2, 2),
 }
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+# Models described by a config.json (a folder with config.json + model.safetensors). `architecture` selects the reader here and the
+# model class in simplellminference_b200.models; the Llama shapes above stay what the C engine takes.
+# ---------------------------------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RotaryConfig:
+    """Rotary positions on the first ``dims`` dimensions of a head; ``scaling`` = YaRN-style (factor, original, fast, slow) or None."""
+    dims: int
+    base: float
+    scaling: dict | None = None
+
+
+@dataclass(frozen=True)
+class SoftmaxMixerConfig:
+    heads: int
+    kv_heads: int
+    dim: int          # per-head query / key width
+    vdim: int         # per-head value width
+    scale: float
+    rot: RotaryConfig
+
+
+@dataclass(frozen=True)
+class RecurrentMixerConfig:
+    width: int
+    blocks: int
+    conv: int         # taps of the causal convolution
+
+
+@dataclass(frozen=True)
+class LinearAttentionMixerConfig:
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+
+
+@dataclass(frozen=True)
+class MunazenLayerConfig:
+    type: str                                   # "parallel" | "gla"
+    left: SoftmaxMixerConfig | None = None      # parallel
+    right: RecurrentMixerConfig | None = None   # parallel
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    gla: LinearAttentionMixerConfig | None = None
+    ff: int | None = None                       # width of the dense feed-forward, None = the layer has none
+
+
+@dataclass(frozen=True)
+class MunazenConfig:
+    """The Munazen design: every size and every constant that may differ between its models comes from config.json."""
+    architecture: str
+    vocab: int
+    width: int
+    streams: int
+    norm_eps: float
+    norm_groups: int
+    layers: tuple
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+
+    @staticmethod
+    def from_dict(c: dict) -> "MunazenConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            m, mlp = l["mixer"], l.get("mlp")
+            if mlp is not None and mlp.get("kind", "dense") != "dense":
+                raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")
+            ff = int(mlp["ff"]) if mlp is not None else None
+            if l["type"] == "parallel":
+                a, r = m["left"], m["right"]
+                rot = a["rot"]
+                layers.append(MunazenLayerConfig(
+                    "parallel",
+                    left=SoftmaxMixerConfig(int(a["heads"]), int(a["kv_heads"]), int(a["dim"]), int(a["vdim"]), float(a["scale"]),
+                                            RotaryConfig(int(rot["dims"]), float(rot["base"]), rot.get("scaling") or None)),
+                    right=RecurrentMixerConfig(int(r["width"]), int(r["blocks"]), int(r["conv"])),
+                    left_scale=float(m["left_scale"]), right_scale=float(m["right_scale"]), ff=ff))
+            elif l["type"] == "gla":
+                layers.append(MunazenLayerConfig("gla", gla=LinearAttentionMixerConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]), float(m["tau"])),
+                                                 ff=ff))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {l['type']!r}")
+        loop = c.get("loop") or {}
+        start, stop, times = int(loop.get("start", 0)), int(loop.get("stop", 0)), int(loop.get("times", 1))
+        if not (0 <= start <= stop <= len(layers)) or times < 1:
+            raise ValueError(f"loop {loop} does not fit {len(layers)} layers")
+        norm = c.get("norm") or {}
+        return MunazenConfig(c["architecture"], int(c["vocab"]), int(c["width"]), int(c.get("streams", 1)), float(norm.get("eps", 1e-6)),
+                             int(norm.get("groups", 1)), tuple(layers), start, stop, times)
+
+    def layer_runs(self) -> list:
+        """Layer indices in the order they run: the looped range repeats with the same weights (each pass has its own state)."""
+        return (list(range(self.loop_start)) + list(range(self.loop_start, self.loop_stop)) * self.loop_times
+                + list(range(self.loop_stop, len(self.layers))))
+
+
+CONFIG_READERS = {"Munazen": MunazenConfig.from_dict}
+
+
+def read_model_config(model_dir: str):
+    """config.json of a model folder -> the config object of its architecture (KeyError names the architectures known here)."""
+    import json
+    import os
+    with open(os.path.join(model_dir, "config.json")) as f:
+        c = json.load(f)
+    arch = c.get("architecture")
+    if arch not in CONFIG_READERS:
+        raise KeyError(f"architecture {arch!r} is not registered (known: {sorted(CONFIG_READERS)})")
+    return CONFIG_READERS[arch](c)

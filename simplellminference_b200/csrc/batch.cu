@@ -24,78 +24,11 @@
 #include <vector>
 
 #include "batch_gemv.cuh"
+#include "kvpages.cuh"
 #include "engine_view.cuh"
 #include "prefill.cuh"
 
 using namespace sllm;
-
-// ---------------------------------------------------------------------------------------- page bookkeeping ---
-struct sllm_kvpages {
-    int n_pages = 0, page_len = 0, max_seqs = 0, max_pages = 0;
-    std::vector<int32_t> free_;    // stack of free page ids; page 0 is handed out first
-    std::vector<int32_t> table;    // [max_seqs][max_pages], -1 = none
-    std::vector<int32_t> held;     // pages held by each sequence
-
-    int pages_for(int n_positions) const { return (n_positions + page_len - 1) / page_len; }
-    // pages a sequence would have to take to cover positions [0, n_positions); < 0: it cannot (beyond max_pages)
-    int extra_needed(int seq, int n_positions) const {
-        const int need = pages_for(n_positions);
-        if (need > max_pages) return -1;
-        return std::max(0, need - held[seq]);
-    }
-    void take(int seq, int extra) {
-        for (int i = 0; i < extra; ++i) {
-            table[(size_t)seq * max_pages + held[seq]++] = free_.back();
-            free_.pop_back();
-        }
-    }
-    void release(int seq) {
-        for (int i = held[seq] - 1; i >= 0; --i) {   // so that the pages come back in the order they were handed out
-            free_.push_back(table[(size_t)seq * max_pages + i]);
-            table[(size_t)seq * max_pages + i] = -1;
-        }
-        held[seq] = 0;
-    }
-};
-
-extern "C" {
-
-sllm_kvpages* sllm_kvpages_create(int32_t n_pages, int32_t page_len, int32_t max_seqs, int32_t max_pages_per_seq) {
-    if (n_pages < 1 || page_len < 1 || max_seqs < 1 || max_pages_per_seq < 1) {
-        set_error("kvpages: n_pages=%d page_len=%d max_seqs=%d max_pages_per_seq=%d must all be positive", n_pages, page_len, max_seqs, max_pages_per_seq);
-        return nullptr;
-    }
-    auto* kp = new sllm_kvpages();
-    kp->n_pages = n_pages; kp->page_len = page_len; kp->max_seqs = max_seqs; kp->max_pages = max_pages_per_seq;
-    kp->free_.resize(n_pages);
-    for (int i = 0; i < n_pages; ++i) kp->free_[i] = n_pages - 1 - i;
-    kp->table.assign((size_t)max_seqs * max_pages_per_seq, -1);
-    kp->held.assign(max_seqs, 0);
-    return kp;
-}
-
-void sllm_kvpages_destroy(sllm_kvpages* kp) { delete kp; }
-
-int32_t sllm_kvpages_reserve(sllm_kvpages* kp, int32_t seq, int32_t n_positions) {
-    SLLM_REQUIRE(kp && seq >= 0 && seq < kp->max_seqs && n_positions >= 0, SLLM_EINVAL, "kvpages_reserve: bad argument (seq %d, positions %d)", seq, n_positions);
-    const int extra = kp->extra_needed(seq, n_positions);
-    SLLM_REQUIRE(extra >= 0, SLLM_EINVAL, "kvpages_reserve: %d positions need more than %d pages of %d", n_positions, kp->max_pages, kp->page_len);
-    SLLM_REQUIRE(extra <= (int)kp->free_.size(), SLLM_ENOMEM, "out of KV pages: sequence %d needs %d more, %d free", seq, extra, (int)kp->free_.size());
-    kp->take(seq, extra);
-    return extra;
-}
-
-int sllm_kvpages_release(sllm_kvpages* kp, int32_t seq) {
-    SLLM_REQUIRE(kp && seq >= 0 && seq < kp->max_seqs, SLLM_EINVAL, "kvpages_release: bad sequence %d", seq);
-    kp->release(seq);
-    return SLLM_OK;
-}
-
-int32_t sllm_kvpages_free_count(const sllm_kvpages* kp) { return kp ? (int32_t)kp->free_.size() : 0; }
-int32_t sllm_kvpages_held(const sllm_kvpages* kp, int32_t seq) { return (kp && seq >= 0 && seq < kp->max_seqs) ? kp->held[seq] : 0; }
-const int32_t* sllm_kvpages_table(const sllm_kvpages* kp) { return kp ? kp->table.data() : nullptr; }
-
-}  // extern "C"
 
 // ------------------------------------------------------------------------------------------------ the batch ---
 constexpr int kBatchMaxSeqs = 64;

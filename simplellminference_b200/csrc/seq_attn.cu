@@ -1,0 +1,302 @@
+// csrc/seq_attn.cu — softmax attention of the ragged token batch over a paged cache, for portions of prompts and single decoded tokens in
+// one launch: rotary positions on q / k (partial, interleaved or half-split pairs, scaled frequencies arrive as a table), values rotated by
+// their own position before they are cached and turned back by the query's position afterwards, key and value heads of different widths,
+// grouped query heads, a sigmoid gate per head. Scores, softmax weights and the weighted sum are fp32 whatever the cache holds.
+//
+// seq_attention_kernel: CTA = (tile of up to 32 consecutive queries of one segment, query head, share of the key tiles), 8 warps x 4
+// queries. A tile of 32 keys and values of the head's kv head is staged in shared memory (fp32); a lane owns one key for the scores
+// (16-byte shared loads, rows padded by 4 floats: conflict-free) and dv/32 output columns for the weighted sum; online softmax per query
+// with warp reductions. The key tiles are dealt to `nsplit` CTAs in turn (long contexts with few queries: decode), every CTA leaves
+// (max, sum, unnormalised output) and seq_attention_finish_kernel merges them.
+#include "seq_common.cuh"
+
+namespace sllm {
+
+// cos and sin of pos * freq. The product is formed and reduced in double: at position 1000 an fp32 product is already off by up to
+// 3e-5 rad, five hundred times the rounding of everything else in the layer, and the error would grow with the position.
+__device__ __forceinline__ void seq_angle(int pos, double freq, float* sn, float* cs) {
+    double s, c;
+    sincos((double)pos * freq, &s, &c);
+    *sn = (float)s;
+    *cs = (float)c;
+}
+
+constexpr int kBQ = 32, kBK = 32, kQW = 4;   // queries per CTA, keys per tile, queries per warp
+constexpr int kMaxDvChunks = 8;              // dv <= 256
+
+struct AttnArgs {
+    sllm_seq_batch b;
+    const float* q; int ldq, heads, kv_heads, dk, dv; float scale;
+    const void *k_pool, *v_pool;
+    int nsplit; float* ws;
+};
+
+template <typename KV>
+__global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
+    extern __shared__ __align__(16) float sm[];
+    const int dk = p.dk, dv = p.dv, dkp = ((dk + 3) & ~3) + 4;   // padded row of q / k in floats
+    float* sq = sm;                      // [kBQ][dkp]
+    float* sk = sq + kBQ * dkp;          // [kBK][dkp]
+    float* sv = sk + kBK * dkp;          // [kBK][dv]
+    const sllm_seq_batch& b = p.b;
+    const int qt = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    const int seg = b.qt_seg[qt], off = b.qt_off[qt];
+    const int nq = min(kBQ, b.seg_len[seg] - off), t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
+    const int g = h / (p.heads / p.kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const KV* kp = reinterpret_cast<const KV*>(p.k_pool);
+    const KV* vp = reinterpret_cast<const KV*>(p.v_pool);
+
+    for (int i = threadIdx.x; i < kBQ * dkp; i += blockDim.x) {
+        const int r = i / dkp, c = i % dkp;
+        sq[i] = (r < nq && c < dk) ? p.q[(size_t)(t0 + r) * p.ldq + (size_t)h * dk + c] : 0.0f;
+    }
+    float m[kQW], l[kQW], acc[kQW][kMaxDvChunks];
+#pragma unroll
+    for (int i = 0; i < kQW; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < kMaxDvChunks; ++c) acc[i][c] = 0.0f;
+    }
+    const int last_pos = pos0 + nq - 1, nkt = last_pos / kBK + 1;
+    for (int kt = split; kt < nkt; kt += p.nsplit) {
+        const int j0 = kt * kBK;
+        const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
+        const int valid = min(kBK, last_pos + 1 - j0);   // keys of this tile that exist
+        __syncthreads();
+        const size_t krow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dv);
+        for (int i = threadIdx.x; i < kBK * dkp; i += blockDim.x) {
+            const int r = i / dkp, c = i % dkp;
+            sk[i] = (r < valid && c < dk) ? seq_ld(kp, krow + (size_t)r * dk + c) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < kBK * dv; i += blockDim.x) {
+            const int r = i / dv;
+            sv[i] = r < valid ? seq_ld(vp, vrow + i) : 0.0f;
+        }
+        __syncthreads();
+        // scores: lane = key j0 + lane, four queries of this warp
+        float s[kQW] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float* krowp = sk + lane * dkp;
+        for (int c = 0; c < dk; c += 4) {
+            const float4 kv = *reinterpret_cast<const float4*>(krowp + c);
+#pragma unroll
+            for (int i = 0; i < kQW; ++i) {
+                const float4 qv = *reinterpret_cast<const float4*>(sq + (warp * kQW + i) * dkp + c);
+                s[i] = fmaf(qv.x, kv.x, s[i]);
+                s[i] = fmaf(qv.y, kv.y, s[i]);
+                s[i] = fmaf(qv.z, kv.z, s[i]);
+                s[i] = fmaf(qv.w, kv.w, s[i]);
+            }
+        }
+        float pw[kQW];
+#pragma unroll
+        for (int i = 0; i < kQW; ++i) {
+            const int qi = warp * kQW + i;
+            const bool see = qi < nq && (j0 + lane) <= (pos0 + qi);
+            const float sc = see ? s[i] * p.scale : -INFINITY;
+            const float mn = fmaxf(m[i], warp_max(sc));
+            const float corr = (mn == -INFINITY) ? 1.0f : expf(m[i] - mn);   // m = -inf: nothing accumulated yet, expf(-inf) = 0 is right too
+            pw[i] = see ? expf(sc - mn) : 0.0f;
+            l[i] = l[i] * corr + warp_sum(pw[i]);
+            m[i] = mn;
+#pragma unroll
+            for (int c = 0; c < kMaxDvChunks; ++c) acc[i][c] *= corr;
+        }
+        for (int jj = 0; jj < valid; ++jj) {
+            float pj[kQW];
+#pragma unroll
+            for (int i = 0; i < kQW; ++i) pj[i] = __shfl_sync(0xffffffffu, pw[i], jj);
+#pragma unroll
+            for (int c = 0; c < kMaxDvChunks; ++c) {
+                if (c * 32 < dv) {
+                    const int col = c * 32 + lane;
+                    const float vv = col < dv ? sv[jj * dv + col] : 0.0f;
+#pragma unroll
+                    for (int i = 0; i < kQW; ++i) acc[i][c] = fmaf(pj[i], vv, acc[i][c]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kQW; ++i) {
+        const int qi = warp * kQW + i;
+        if (qi >= nq) continue;
+        float* rec = p.ws + (((size_t)(t0 + qi) * p.heads + h) * p.nsplit + split) * (dv + 2);
+        if (lane == 0) {
+            rec[0] = m[i];
+            rec[1] = l[i];
+        }
+#pragma unroll
+        for (int c = 0; c < kMaxDvChunks; ++c) {
+            const int col = c * 32 + lane;
+            if (col < dv) rec[2 + col] = acc[i][c];
+        }
+    }
+}
+
+// one warp per (token, head): merge the shares, normalise, turn back by the token's position, gate
+__global__ void seq_attention_finish_kernel(sllm_seq_batch b, const float* __restrict__ ws, int nsplit, int heads, int dv, const double* __restrict__ vfreq,
+                                            int layout, const float* __restrict__ gate, int ldg, float* __restrict__ out, int ldo) {
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= b.T * heads) return;
+    const int t = item / heads, h = item % heads;
+    const float* rec = ws + ((size_t)t * heads + h) * nsplit * (dv + 2);
+    float mx = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, rec[(size_t)s * (dv + 2)]);
+    float den = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = rec[(size_t)s * (dv + 2)];
+        if (ms != -INFINITY) den += rec[(size_t)s * (dv + 2) + 1] * expf(ms - mx);
+    }
+    const float gv = gate ? seq_sigmoid(gate[(size_t)t * ldg + h]) : 1.0f;
+    const int pos = b.tok_pos[t];
+    float* orow = out + (size_t)t * ldo + (size_t)h * dv;
+    auto merged = [&](int col) {
+        float v = 0.0f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float ms = rec[(size_t)s * (dv + 2)];
+            if (ms != -INFINITY) v += rec[(size_t)s * (dv + 2) + 2 + col] * expf(ms - mx);
+        }
+        return v / den;
+    };
+    if (!vfreq) {
+        for (int col = lane; col < dv; col += 32) orow[col] = merged(col) * gv;
+        return;
+    }
+    const int half = dv / 2;
+    for (int mi = lane; mi < half; mi += 32) {
+        const int ia = layout == 0 ? 2 * mi : mi, ib = layout == 0 ? 2 * mi + 1 : mi + half;
+        const float u = merged(ia), v = merged(ib);
+        float sn, cs;
+        seq_angle(pos, vfreq[mi], &sn, &cs);
+        orow[ia] = (u * cs + v * sn) * gv;    // rotation by the negative angle
+        orow[ib] = (v * cs - u * sn) * gv;
+    }
+}
+
+// one CTA per token: rotate q in place, rotate k and v and store them into the pools
+template <typename KV>
+__global__ void seq_rotary_kv_kernel(sllm_seq_batch b, float* __restrict__ q, int ldq, int heads, int dk, const float* __restrict__ k, int ldk, int kv_heads,
+                                     const float* __restrict__ v, int ldv, int dv, const double* __restrict__ freq, int n_freq, float magnitude,
+                                     const double* __restrict__ vfreq, int layout, KV* __restrict__ k_pool, KV* __restrict__ v_pool) {
+    const int t = blockIdx.x, posi = b.tok_pos[t], slot = b.tok_slot[t];
+    const int pos = posi;
+    const int page = b.block_table[(size_t)slot * b.max_pages + posi / b.page_len], in_page = posi % b.page_len;
+    const int rd = 2 * n_freq, rhalf = n_freq;
+    // q: heads * (dk/2 rounded up) work items; pairs beyond the rotary dimensions pass unchanged (they stay in place)
+    for (int i = threadIdx.x; i < heads * n_freq; i += blockDim.x) {
+        const int h = i / n_freq, mi = i % n_freq;
+        const int ia = layout == 0 ? 2 * mi : mi, ib = layout == 0 ? 2 * mi + 1 : mi + rhalf;
+        float sn, cs;
+        seq_angle(pos, freq[mi], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
+        float* qh = q + (size_t)t * ldq + (size_t)h * dk;
+        const float u = qh[ia], w = qh[ib];
+        qh[ia] = u * cs - w * sn;
+        qh[ib] = w * cs + u * sn;
+    }
+    for (int i = threadIdx.x; i < kv_heads * dk; i += blockDim.x) {
+        const int g = i / dk, c = i % dk;
+        const float* kh = k + (size_t)t * ldk + (size_t)g * dk;
+        float val = kh[c];
+        if (c < rd) {
+            int mi, first;
+            if (layout == 0) { mi = c >> 1; first = !(c & 1); } else { mi = c < rhalf ? c : c - rhalf; first = c < rhalf; }
+            const int partner = layout == 0 ? (c ^ 1) : (first ? c + rhalf : c - rhalf);
+            float sn, cs;
+            seq_angle(pos, freq[mi], &sn, &cs);
+            sn *= magnitude;
+            cs *= magnitude;
+            val = first ? kh[c] * cs - kh[partner] * sn : kh[c] * cs + kh[partner] * sn;
+        }
+        seq_st(k_pool, seq_pool_row(page, kv_heads, g, b.page_len, in_page, dk) + c, val);
+    }
+    const int vhalf = dv / 2;
+    for (int i = threadIdx.x; i < kv_heads * dv; i += blockDim.x) {
+        const int g = i / dv, c = i % dv;
+        const float* vh = v + (size_t)t * ldv + (size_t)g * dv;
+        float val = vh[c];
+        if (vfreq) {
+            int mi, first;
+            if (layout == 0) { mi = c >> 1; first = !(c & 1); } else { mi = c < vhalf ? c : c - vhalf; first = c < vhalf; }
+            const int partner = layout == 0 ? (c ^ 1) : (first ? c + vhalf : c - vhalf);
+            float sn, cs;
+            seq_angle(pos, vfreq[mi], &sn, &cs);
+            val = first ? vh[c] * cs - vh[partner] * sn : vh[c] * cs + vh[partner] * sn;
+        }
+        seq_st(v_pool, seq_pool_row(page, kv_heads, g, b.page_len, in_page, dv) + c, val);
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+static int check_batch(const sllm_seq_batch* b, const char* who) {
+    SLLM_REQUIRE(b && b->T > 0 && b->nseg > 0 && b->tok_slot && b->tok_pos && b->seg_start && b->seg_len && b->seg_slot && b->seg_pos0, SLLM_EINVAL,
+                 "%s: incomplete batch description", who);
+    return SLLM_OK;
+}
+
+extern "C" {
+
+int sllm_seq_rotary_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk, int32_t kv_heads,
+                       const float* v, int32_t ldv, int32_t dv, const double* freq, int32_t n_freq, float magnitude, const double* vfreq, int32_t layout,
+                       void* k_pool, void* v_pool, int32_t kv_dtype, sllm_stream_t stream) {
+    if (int rc = check_batch(b, "seq_rotary_kv")) return rc;
+    SLLM_REQUIRE(q && k && v && k_pool && v_pool && b->block_table && heads > 0 && kv_heads > 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_rotary_kv: bad argument");
+    SLLM_REQUIRE(n_freq >= 0 && 2 * n_freq <= dk && (n_freq == 0 || freq), SLLM_EINVAL, "seq_rotary_kv: %d rotary pairs do not fit %d dimensions", n_freq, dk);
+    SLLM_REQUIRE(!vfreq || dv % 2 == 0, SLLM_EINVAL, "seq_rotary_kv: rotated values need an even width");
+    SLLM_REQUIRE(layout == 0 || layout == 1, SLLM_EINVAL, "seq_rotary_kv: layout 0 (interleaved) or 1 (halves)");
+    SLLM_REQUIRE(kv_dtype == SLLM_F32 || kv_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_rotary_kv: fp32 or bf16 pools");
+    if (kv_dtype == SLLM_F32)
+        seq_rotary_kv_kernel<float><<<b->T, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, freq, n_freq, magnitude, vfreq,
+                                                                         layout, (float*)k_pool, (float*)v_pool);
+    else
+        seq_rotary_kv_kernel<uint16_t><<<b->T, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, freq, n_freq, magnitude,
+                                                                            vfreq, layout, (uint16_t*)k_pool, (uint16_t*)v_pool);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t kv_heads, int32_t dk, int32_t dv, float scale,
+                       const void* k_pool, const void* v_pool, int32_t kv_dtype, int32_t nsplit, float* ws, sllm_stream_t stream) {
+    if (int rc = check_batch(b, "seq_attention")) return rc;
+    SLLM_REQUIRE(q && k_pool && v_pool && ws && b->block_table && b->qt_seg && b->qt_off && b->n_qtiles > 0, SLLM_EINVAL, "seq_attention: bad argument");
+    SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0, SLLM_EINVAL, "seq_attention: %d query heads over %d kv heads", heads, kv_heads);
+    SLLM_REQUIRE(dv > 0 && dv <= 32 * kMaxDvChunks, SLLM_ENOTSUP, "seq_attention: value width %d beyond %d", dv, 32 * kMaxDvChunks);
+    SLLM_REQUIRE(b->page_len % kBK == 0, SLLM_ENOTSUP, "seq_attention: pages of a multiple of %d positions", kBK);
+    SLLM_REQUIRE(nsplit >= 1 && nsplit <= 65535, SLLM_EINVAL, "seq_attention: nsplit");
+    SLLM_REQUIRE(kv_dtype == SLLM_F32 || kv_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_attention: fp32 or bf16 pools");
+    const int dkp = ((dk + 3) & ~3) + 4;
+    const size_t smem = ((size_t)(kBQ + kBK) * dkp + (size_t)kBK * dv) * sizeof(float);
+    SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes(), SLLM_ENOTSUP, "seq_attention: heads of %d + %d floats need %zu bytes of shared memory", dk, dv, smem);
+    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws};
+    dim3 grid(b->n_qtiles, heads, nsplit);
+    if (kv_dtype == SLLM_F32) {
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        seq_attention_kernel<float><<<grid, 256, smem, as_stream(stream)>>>(p);
+    } else {
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        seq_attention_kernel<uint16_t><<<grid, 256, smem, as_stream(stream)>>>(p);
+    }
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_attention_finish(const sllm_seq_batch* b, const float* ws, int32_t nsplit, int32_t heads, int32_t dv, const double* vfreq, int32_t layout,
+                              const float* gate, int32_t ldg, float* out, int32_t ldo, sllm_stream_t stream) {
+    if (int rc = check_batch(b, "seq_attention_finish")) return rc;
+    SLLM_REQUIRE(ws && out && nsplit >= 1 && heads > 0 && dv > 0 && (!vfreq || dv % 2 == 0), SLLM_EINVAL, "seq_attention_finish: bad argument");
+    const int items = b->T * heads;
+    seq_attention_finish_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(*b, ws, nsplit, heads, dv, vfreq, layout, gate, ldg, out, ldo);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+}  // extern "C"

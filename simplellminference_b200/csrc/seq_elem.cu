@@ -1,0 +1,173 @@
+// csrc/seq_elem.cu — row-wise building blocks of the ragged token batch (sllm_seq_*): embedding into residual streams, the
+// hyper-connection read (weighted sum of the streams + grouped RMS norm) and write (stream mixing + sublayer output), PolyNorm,
+// row gather and the per-head norm with a SiLU gate. Everything here is fp32: norms and the residual sum are never rounded.
+#include "seq_common.cuh"
+
+namespace sllm {
+
+__global__ void seq_embed_kernel(const int32_t* __restrict__ ids, const void* __restrict__ table, int w_dtype, int vocab, int d, int streams,
+                                 float* __restrict__ out, int T) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = seq_ldw(table, w_dtype, (size_t)id * d + j);
+        for (int s = 0; s < streams; ++s) out[((size_t)s * T + t) * d + j] = v;
+    }
+}
+
+// grid (T, groups): one CTA normalises one part of one token's vector
+__global__ void seq_hyper_read_kernel(const float* __restrict__ x, int streams, int T, int d, const float* __restrict__ coef,
+                                      const float* __restrict__ norm_w, int groups, float eps, float* __restrict__ y) {
+    __shared__ float red[33];
+    const int t = blockIdx.x, g = blockIdx.y, n = d / groups, j0 = g * n;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float u = 0.0f;
+        for (int s = 0; s < streams; ++s) u = fmaf(coef ? coef[s] : 1.0f, x[((size_t)s * T + t) * d + j0 + j], u);
+        y[(size_t)t * d + j0 + j] = u;
+        ss = fmaf(u, u, ss);
+    }
+    if (!norm_w) return;
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {   // each thread re-reads what it wrote itself
+        const size_t i = (size_t)t * d + j0 + j;
+        y[i] = (y[i] * inv) * norm_w[j0 + j];
+    }
+}
+
+constexpr int kMaxStreams = 8;
+
+__global__ void seq_hyper_write_kernel(float* __restrict__ x, int streams, int T, int d, const float* __restrict__ mix,
+                                       const float* __restrict__ outc, const float* __restrict__ y) {
+    const size_t n = (size_t)T * d;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float old[kMaxStreams];
+        for (int s = 0; s < streams; ++s) old[s] = x[(size_t)s * n + i];
+        const float yv = y[i];
+        for (int to = 0; to < streams; ++to) {
+            float v;
+            if (mix) {
+                v = 0.0f;
+                for (int s = 0; s < streams; ++s) v = fmaf(mix[s * streams + to], old[s], v);
+            } else {
+                v = old[to];
+            }
+            x[(size_t)to * n + i] = fmaf(outc ? outc[to] : 1.0f, yv, v);
+        }
+    }
+}
+
+__global__ void seq_polynorm_kernel(const float* z, int ldz, const float* __restrict__ coef, float eps, float* out,
+                                    int ldo, int n) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const float* zr = z + (size_t)t * ldz;
+    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const float v = zr[j], v2 = v * v, v3 = v2 * v;
+        s1 = fmaf(v, v, s1);
+        s2 = fmaf(v2, v2, s2);
+        s3 = fmaf(v3, v3, s3);
+    }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    s3 = block_sum(s3, red);
+    const float i1 = 1.0f / sqrtf(s1 / (float)n + eps), i2 = 1.0f / sqrtf(s2 / (float)n + eps), i3 = 1.0f / sqrtf(s3 / (float)n + eps);
+    const float c0 = coef[0], c1 = coef[1], c2 = coef[2], c3 = coef[3];
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const float v = zr[j], v2 = v * v, v3 = v2 * v;
+        out[(size_t)t * ldo + j] = c0 * (v * i1) + c1 * (v2 * i2) + c2 * (v3 * i3) + c3;
+    }
+}
+
+__global__ void seq_gather_rows_kernel(const float* __restrict__ x, int ldx, const int32_t* __restrict__ rows, int d, float* __restrict__ out) {
+    const int i = blockIdx.x;
+    const float* src = x + (size_t)rows[i] * ldx;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) out[(size_t)i * d + j] = src[j];
+}
+
+// one warp per (token, head)
+__global__ void seq_headnorm_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg, const float* __restrict__ w,
+                                         int heads, int dv, float eps, float* __restrict__ out, int ldout, int T) {
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= T * heads) return;
+    const int t = item / heads, h = item % heads;
+    const float* orow = o + (size_t)t * ldo + (size_t)h * dv;
+    float ss = 0.0f;
+    for (int j = lane; j < dv; j += 32) ss = fmaf(orow[j], orow[j], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+    for (int j = lane; j < dv; j += 32) {
+        const float gv = g[(size_t)t * ldg + (size_t)h * dv + j];
+        out[(size_t)t * ldout + (size_t)h * dv + j] = ((orow[j] * inv) * w[j]) * (gv / (1.0f + expf(-gv)));
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+extern "C" {
+
+int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32_t vocab, int32_t d, int32_t streams, float* out, int32_t T,
+                   sllm_stream_t stream) {
+    SLLM_REQUIRE(ids && table && out && T > 0 && d > 0 && vocab > 0 && streams >= 1, SLLM_EINVAL, "seq_embed: bad argument");
+    SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_embed: fp32 or bf16 tables");
+    seq_embed_kernel<<<T, 128, 0, as_stream(stream)>>>(ids, table, w_dtype, vocab, d, streams, out, T);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_hyper_read(const float* x, int32_t streams, int32_t T, int32_t d, const float* coef, const float* norm_w, int32_t groups, float eps,
+                        float* y, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && y && T > 0 && d > 0 && streams >= 1, SLLM_EINVAL, "seq_hyper_read: bad argument");
+    if (!norm_w) groups = 1;
+    SLLM_REQUIRE(groups >= 1 && d % groups == 0, SLLM_EINVAL, "seq_hyper_read: %d does not divide into %d parts", d, groups);
+    const int n = d / groups, threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+    seq_hyper_read_kernel<<<dim3(T, groups), threads, 0, as_stream(stream)>>>(x, streams, T, d, coef, norm_w, groups, eps, y);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_hyper_write(float* x, int32_t streams, int32_t T, int32_t d, const float* mix, const float* outc, const float* y, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && y && T > 0 && d > 0, SLLM_EINVAL, "seq_hyper_write: bad argument");
+    SLLM_REQUIRE(streams >= 1 && streams <= kMaxStreams, SLLM_ENOTSUP, "seq_hyper_write: 1..%d streams", kMaxStreams);
+    const size_t n = (size_t)T * d;
+    const int blocks = (int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8);
+    seq_hyper_write_kernel<<<blocks, 256, 0, as_stream(stream)>>>(x, streams, T, d, mix, outc, y);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_polynorm(const float* z, int32_t ldz, const float* coef, float eps, float* out, int32_t ldo, int32_t T, int32_t n, sllm_stream_t stream) {
+    SLLM_REQUIRE(z && coef && out && T > 0 && n > 0 && ldz >= n && ldo >= n, SLLM_EINVAL, "seq_polynorm: bad argument");
+    seq_polynorm_kernel<<<T, n >= 2048 ? 512 : 256, 0, as_stream(stream)>>>(z, ldz, coef, eps, out, ldo, n);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_gather_rows(const float* x, int32_t ldx, const int32_t* rows, int32_t n, int32_t d, float* out, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && rows && out && n > 0 && d > 0, SLLM_EINVAL, "seq_gather_rows: bad argument");
+    seq_gather_rows_kernel<<<n, 128, 0, as_stream(stream)>>>(x, ldx, rows, d, out);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t ldg, const float* w, int32_t heads, int32_t dv, float eps, float* out,
+                           int32_t ldout, int32_t T, sllm_stream_t stream) {
+    SLLM_REQUIRE(o && g && w && out && heads > 0 && dv > 0 && T > 0, SLLM_EINVAL, "seq_headnorm_gate: bad argument");
+    const int items = T * heads;
+    seq_headnorm_gate_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, T);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,236 @@
+// csrc/seq_linear.cu — sllm_seq_linear: C = alpha * (A . W^T + bias) (+ C) for the ragged token batch. Three bodies:
+//   * rows_kernel  (T <= 8, decode-sized steps): one warp per output column streams that weight row once with 16-byte loads and keeps one
+//     accumulator per activation row — bandwidth-bound like the GEMV of the one-sequence path, any shape (scalar loads when unaligned);
+//   * tile_kernel  (any shape): 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMAs with fp32 accumulation. This is
+//     the body of the all-fp32 mode, and of bf16 products whose shape the tensor-core tiles do not take;
+//   * the tcgen05 GEMM of the prefill path (prefill_gemm.cu) for bf16 weights when the caller passes a bf16 scratch for A and the shape
+//     fits its TMA boxes; bias, alpha and accumulation then run as a short epilogue kernel over C.
+// In bf16 mode (round_a) the activations are rounded to bf16 as they are loaded, so all three bodies multiply the same operands and
+// differ only in summation order.
+#include "prefill.cuh"
+#include "seq_common.cuh"
+
+namespace sllm {
+
+struct LinArgs {
+    const float* A; const void* W; const float* bias; float* C;
+    int lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a;
+    float alpha;
+    long long a_bs, w_bs, bias_bs, c_bs;
+};
+
+constexpr int kRowsMax = 8;
+
+template <int WD>
+__global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec) {
+    const int b = blockIdx.y;
+    const float* A = p.A + (size_t)b * p.a_bs;
+    const float* bias = p.bias ? p.bias + (size_t)b * p.bias_bs : nullptr;
+    float* C = p.C + (size_t)b * p.c_bs;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= p.N) return;
+    float acc[kRowsMax];
+#pragma unroll
+    for (int t = 0; t < kRowsMax; ++t) acc[t] = 0.0f;
+    if (WD == SLLM_BF16) {
+        const uint16_t* w = reinterpret_cast<const uint16_t*>(p.W) + (size_t)b * p.w_bs + (size_t)n * p.ldw;
+        if (vec) {
+            for (int k = lane * 8; k < p.K; k += 256) {
+                const uint4 u = ldg_stream(w + k);
+                const float wv[8] = {bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y), bf16_lo(u.z), bf16_hi(u.z), bf16_lo(u.w), bf16_hi(u.w)};
+#pragma unroll
+                for (int t = 0; t < kRowsMax; ++t) {
+                    if (t < p.T) {
+                        const float4 a0 = *reinterpret_cast<const float4*>(A + (size_t)t * p.lda + k);
+                        const float4 a1 = *reinterpret_cast<const float4*>(A + (size_t)t * p.lda + k + 4);
+                        float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[t] = fmaf(p.round_a ? seq_round_bf16(av[e]) : av[e], wv[e], acc[t]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < p.K; k += 32) {
+                const float wv = seq_ld(w, k);
+#pragma unroll
+                for (int t = 0; t < kRowsMax; ++t)
+                    if (t < p.T) {
+                        const float a = A[(size_t)t * p.lda + k];
+                        acc[t] = fmaf(p.round_a ? seq_round_bf16(a) : a, wv, acc[t]);
+                    }
+            }
+        }
+    } else {
+        const float* w = reinterpret_cast<const float*>(p.W) + (size_t)b * p.w_bs + (size_t)n * p.ldw;
+        if (vec) {
+            for (int k = lane * 4; k < p.K; k += 128) {
+                const uint4 u = ldg_stream(w + k);
+                const float wv[4] = {__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w)};
+#pragma unroll
+                for (int t = 0; t < kRowsMax; ++t) {
+                    if (t < p.T) {
+                        const float4 a0 = *reinterpret_cast<const float4*>(A + (size_t)t * p.lda + k);
+                        acc[t] = fmaf(a0.x, wv[0], acc[t]);
+                        acc[t] = fmaf(a0.y, wv[1], acc[t]);
+                        acc[t] = fmaf(a0.z, wv[2], acc[t]);
+                        acc[t] = fmaf(a0.w, wv[3], acc[t]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < p.K; k += 32) {
+                const float wv = w[k];
+#pragma unroll
+                for (int t = 0; t < kRowsMax; ++t)
+                    if (t < p.T) acc[t] = fmaf(A[(size_t)t * p.lda + k], wv, acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < kRowsMax; ++t) {
+        if (t < p.T) {
+            const float s = warp_sum(acc[t]);
+            if (lane == 0) {
+                float v = p.alpha * (s + (bias ? bias[n] : 0.0f));
+                float* c = C + (size_t)t * p.ldc + n;
+                *c = p.accumulate ? *c + v : v;
+            }
+        }
+    }
+}
+
+constexpr int kTM = 64, kTN = 64, kTK = 16;
+
+template <int WD>
+__global__ void __launch_bounds__(256) seq_linear_tile_kernel(LinArgs p) {
+    __shared__ float As[kTK][kTM + 4];
+    __shared__ float Ws[kTK][kTN + 4];
+    const int b = blockIdx.z;
+    const float* A = p.A + (size_t)b * p.a_bs;
+    const float* bias = p.bias ? p.bias + (size_t)b * p.bias_bs : nullptr;
+    float* C = p.C + (size_t)b * p.c_bs;
+    const int m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;   // loader: row lr of the tile, k columns lk .. lk+3
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < p.K; k0 += kTK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = k0 + lk + e;
+            float a = 0.0f, w = 0.0f;
+            if (k < p.K) {
+                if (m0 + lr < p.T) {
+                    a = A[(size_t)(m0 + lr) * p.lda + k];
+                    if (p.round_a) a = seq_round_bf16(a);
+                }
+                if (n0 + lr < p.N) {
+                    const size_t wi = (size_t)b * p.w_bs + (size_t)(n0 + lr) * p.ldw + k;
+                    w = WD == SLLM_BF16 ? seq_ld(reinterpret_cast<const uint16_t*>(p.W), wi) : reinterpret_cast<const float*>(p.W)[wi];
+                }
+            }
+            As[lk + e][lr] = a;
+            Ws[lk + e][lr] = w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kTK; ++k) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 wv = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+            const float a4[4] = {av.x, av.y, av.z, av.w}, w4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a4[i], w4[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= p.T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= p.N) continue;
+            const float v = p.alpha * (acc[i][j] + (bias ? bias[n] : 0.0f));
+            float* c = C + (size_t)m * p.ldc + n;
+            *c = p.accumulate ? *c + v : v;
+        }
+    }
+}
+
+// A (fp32, row stride lda) -> bf16 [T][K] dense
+__global__ void seq_to_bf16_kernel(const float* __restrict__ A, int lda, uint16_t* __restrict__ out, int T, int K) {
+    const size_t n = (size_t)T * K;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / K, k = i % K;
+        out[i] = f32_to_bf16_bits(A[t * lda + k]);
+    }
+}
+
+// C = alpha * (P + bias) (+ C) where P [T][N] dense holds the plain product
+__global__ void seq_linear_epilogue_kernel(const float* __restrict__ P, const float* __restrict__ bias, float* __restrict__ C, int ldc, int T, int N,
+                                           float alpha, int accumulate) {
+    const size_t n = (size_t)T * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / N, j = i % N;
+        const float v = alpha * (P[i] + (bias ? bias[j] : 0.0f));
+        float* c = C + t * ldc + j;
+        *c = accumulate ? *c + v : v;
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc, int32_t T,
+                               int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs, int64_t w_bs,
+                               int64_t bias_bs, int64_t c_bs, void* a16, sllm_stream_t stream) {
+    SLLM_REQUIRE(A && W && C && T > 0 && N > 0 && K > 0 && batch >= 1, SLLM_EINVAL, "seq_linear: bad argument");
+    SLLM_REQUIRE(lda >= K && ldw >= K && ldc >= N, SLLM_EINVAL, "seq_linear: row strides shorter than the rows");
+    SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_linear: fp32 or bf16 weights");
+    cudaStream_t st = as_stream(stream);
+    LinArgs p{A, W, bias, C, lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a, alpha, a_bs, w_bs, bias_bs, c_bs};
+    if (T <= kRowsMax) {
+        const int e = w_dtype == SLLM_BF16 ? 8 : 4;   // elements per 16-byte weight load
+        const bool vec = K % e == 0 && ldw % e == 0 && (w_bs % e) == 0 && lda % 4 == 0 && (a_bs % 4) == 0 &&
+                         ((uintptr_t)W % 16) == 0 && ((uintptr_t)A % 16) == 0;
+        dim3 grid((N + 7) / 8, batch);
+        if (w_dtype == SLLM_BF16) seq_linear_rows_kernel<SLLM_BF16><<<grid, 256, 0, st>>>(p, vec);
+        else seq_linear_rows_kernel<SLLM_F32><<<grid, 256, 0, st>>>(p, vec);
+        ++g_launches;
+        SLLM_LAUNCH_CHECK();
+        return SLLM_OK;
+    }
+    // tensor cores: bf16 weights, a dense bf16 copy of A, rows that TMA can address (16-byte multiples) and enough work to fill tiles
+    if (a16 && w_dtype == SLLM_BF16 && batch == 1 && round_a && T >= 64 && N >= 64 && K >= 64 && K % 8 == 0 && ldw == K && N % 4 == 0 &&
+        ((uintptr_t)W % 16) == 0) {
+        static PfCache* cache = pf_cache_create();
+        const size_t n = (size_t)T * K;
+        seq_to_bf16_kernel<<<(int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8), 256, 0, st>>>(A, lda, reinterpret_cast<uint16_t*>(a16), T, K);
+        ++g_launches;
+        SLLM_LAUNCH_CHECK();
+        float* P = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + (((size_t)T * K * 2 + 255) / 256) * 256);   // product scratch behind the bf16 rows
+        PfGemmArgs a{};
+        a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.epilogue = PF_EPI_STORE; a.out = P; a.ld_out = N; a.n_valid = N; a.bn = 0;
+        const int rc = pf_gemm(cache, a, st);
+        if (rc != SLLM_OK) return rc;
+        const size_t m = (size_t)T * N;
+        seq_linear_epilogue_kernel<<<(int)std::min<size_t>((m + 255) / 256, (size_t)sm_count() * 8), 256, 0, st>>>(P, bias, C, ldc, T, N, alpha, accumulate);
+        ++g_launches;
+        SLLM_LAUNCH_CHECK();
+        return SLLM_OK;
+    }
+    dim3 grid((N + kTN - 1) / kTN, (T + kTM - 1) / kTM, batch);
+    if (w_dtype == SLLM_BF16) seq_linear_tile_kernel<SLLM_BF16><<<grid, 256, 0, st>>>(p);
+    else seq_linear_tile_kernel<SLLM_F32><<<grid, 256, 0, st>>>(p);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}

@@ -1,0 +1,206 @@
+"""Sequence-mixing and feed-forward mechanisms over the ragged-token-batch kernels (seqops.Ops), each with its constants as parameters so
+that a model description can combine them: fused input projections, softmax attention with (scaled, partial) rotary positions, rotated
+values and a head gate over a paged cache; a Griffin-style recurrent block (short causal convolution + real-gated linear recurrent unit);
+gated linear attention with a decay per key channel; a PolyNorm feed-forward. A mechanism says which per-sequence state it needs
+(``state_spec``); the engine's state manager owns that memory and hands it to ``forward`` — no mechanism keeps a cache of its own.
+
+Additive to the reference, whose only model is the Llama forward of source/model/model.cpp:40-140."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .config import BF16
+
+F32B = 4   # bytes of an activation
+
+
+def yarn_frequencies(dims: int, base: float, scaling: dict | None):
+    """Angular step per position of each of the dims/2 rotary pairs, and the factor on cos / sin. ``scaling`` = {factor, original, fast,
+    slow}: pairs that turn more than ``fast`` times over the ``original`` context keep their frequency, those that turn less than ``slow``
+    times are slowed down by ``factor``, with a linear ramp over the pair index between the two."""
+    f = [base ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+    out = []
+    for i, fi in enumerate(f):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(fi / factor * ramp + fi * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+class FusedLinear:
+    """Several projections of the same input as ONE product: weight rows concatenated, one bias vector (zeros where a part has none).
+    ``offsets[i]`` is the first output column of part i."""
+
+    def __init__(self, parts, ops, device):
+        self.ops = ops
+        self.K = int(parts[0][0].shape[1])
+        self.sizes = [int(w.shape[0]) for w, _ in parts]
+        self.offsets = [sum(self.sizes[:i]) for i in range(len(parts))]
+        self.N = sum(self.sizes)
+        self.w = torch.cat([w for w, _ in parts], dim=0).contiguous()
+        if any(b is not None for _, b in parts):
+            self.bias = torch.cat([(b.float() if b is not None else torch.zeros(n, device=device)) for (_, b), n in zip(parts, self.sizes)]).contiguous()
+        else:
+            self.bias = None
+
+    def __call__(self, step, a_ptr, lda, c_ptr, ldc, alpha=1.0, accumulate=False):
+        scratch = step.gemm_scratch(self.K, self.N)
+        self.ops.linear(a_ptr, lda, self.w, self.K, self.bias, c_ptr, ldc, step.T, self.N, self.K, step.st, alpha=alpha, accumulate=accumulate,
+                        scratch=scratch)
+
+
+class GatedRotaryAttention:
+    """Causal softmax attention over a paged cache: grouped query heads, key width ``dim`` and value width ``vdim``, rotary positions on
+    the first ``rot.dims`` dimensions of q and k (scaled frequencies), values rotated by their own position before they are cached and the
+    weighted sum turned back by the query's position, one sigmoid gate per head, then the output projection."""
+
+    def __init__(self, cfg, w, pre, ops, device, layout=0):
+        self.cfg, self.ops, self.layout = cfg, ops, layout
+        self.inputs = [(w[pre + "q"], w.get(pre + "q.b")), (w[pre + "k"], w.get(pre + "k.b")), (w[pre + "v"], w.get(pre + "v.b")), (w[pre + "g"], None)]
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        f, self.magnitude = yarn_frequencies(cfg.rot.dims, cfg.rot.base, cfg.rot.scaling)
+        self.freq = torch.tensor(f, dtype=torch.float64, device=device)
+        self.vfreq = torch.tensor([cfg.rot.base ** (-2.0 * m / cfg.vdim) for m in range(cfg.vdim // 2)], dtype=torch.float64, device=device)
+        self.width = cfg.heads * cfg.vdim
+
+    def state_spec(self):
+        return {"pages": [("k", self.cfg.kv_heads, self.cfg.dim), ("v", self.cfg.kv_heads, self.cfg.vdim)], "slots": []}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops = self.cfg, self.ops
+        q, k, v, g = cols
+        ops.rotary_kv(step.b, q, ld, c.heads, c.dim, k, ld, c.kv_heads, v, ld, c.vdim, self.freq, c.rot.dims // 2, self.magnitude, self.vfreq,
+                      self.layout, state["k"], state["v"], step.st)
+        ws = step.scratch("attn_ws", step.T * c.heads * step.nsplit * (c.vdim + 2))
+        ops.attention(step.b, q, ld, c.heads, c.kv_heads, c.dim, c.vdim, c.scale, state["k"], state["v"], step.nsplit, ws, step.st)
+        ops.attention_finish(step.b, ws, step.nsplit, c.heads, c.vdim, self.vfreq, self.layout, g, ld, out, self.width, step.st)
+
+
+class GatedLinearRecurrence:
+    """Griffin's recurrent block: a GELU branch y and a branch u = causal convolution of a projection; per block of channels the gates
+    r = sigmoid(A_r u + b_r), i = sigmoid(A_i u + b_i); log a = -``decay_scale`` * r * softplus(lam); S <- a S + sqrt(1 - a^2) (i * u);
+    the block returns (S * y) projected. State per sequence: S and the last taps-1 inputs of the convolution, fp32."""
+
+    decay_scale = 8.0
+
+    def __init__(self, cfg, w, pre, ops, device):
+        self.cfg, self.ops = cfg, ops
+        self.inputs = [(w[pre + "y"], w.get(pre + "y.b")), (w[pre + "x"], w.get(pre + "x.b"))]
+        self.conv_w = w[pre + "conv"].float().contiguous()
+        self.conv_b = w[pre + "conv.b"].float().contiguous() if pre + "conv.b" in w else None
+        self.gates_w = torch.stack([w[pre + "ra"], w[pre + "ri"]]).contiguous()          # [2][blocks][bs][bs]
+        self.gates_b = torch.stack([w[pre + "ra.b"].float(), w[pre + "ri.b"].float()]).contiguous()   # [2][blocks][bs]
+        self.lam = w[pre + "lam"].float().contiguous()
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.width = cfg.width
+
+    def state_spec(self):
+        slots = [("S", (self.cfg.width,))]
+        if self.cfg.conv > 1:
+            slots.append(("tail", (self.cfg.conv - 1, self.cfg.width)))
+        return {"pages": [], "slots": slots}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T, W = self.cfg, self.ops, step.T, self.cfg.width
+        y, x = cols
+        u = step.scratch("rg_u", T * W)
+        gates = step.scratch("rg_gates", 2 * T * W)          # r logits [T][W], then i logits [T][W]
+        tail = state.get("tail")
+        ops.conv(step.b, x, ld, W, c.conv, self.conv_w, self.conv_b, tail, u, W, step.st)
+        bs = W // c.blocks
+        for which in range(2):   # block-diagonal products: one launch per gate, the blocks as its batch
+            ops.linear(u.data_ptr(), W, self.gates_w[which], bs, self.gates_b[which], gates.data_ptr() + which * T * W * F32B, W, T, bs, bs, step.st,
+                       batch=c.blocks, a_bs=bs, w_bs=bs * bs, bias_bs=bs, c_bs=bs)
+        ops.rglru_scan(step.b, u, W, gates.data_ptr(), gates.data_ptr() + T * W * F32B, W, y, ld, self.lam, self.decay_scale, W, state["S"],
+                       x, ld, c.conv, tail, out, W, step.st)
+
+
+class GatedLinearAttention:
+    """Linear attention with a data-dependent decay per key channel: alpha = sigmoid(W_a2 W_a1 h + b)^(1/tau); per head
+    S <- diag(alpha) S + k v^T, o = S^T (q / sqrt(dim)); o is RMS-normed per head (weight shared by the heads), gated by silu(W_g h) and
+    projected. State per sequence: S [heads][dim][vdim], fp32."""
+
+    def __init__(self, cfg, w, pre, ops, device, eps):
+        self.cfg, self.ops, self.eps = cfg, ops, eps
+        self.inputs = [(w[pre + "q"], None), (w[pre + "k"], None), (w[pre + "v"], None), (w[pre + "g"], None), (w[pre + "a1"], None)]
+        self.a2 = FusedLinear([(w[pre + "a2"], w.get(pre + "a2.b"))], ops, device)
+        self.norm_w = w[pre + "norm"].float().contiguous()
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.width = cfg.heads * cfg.vdim
+
+    def state_spec(self):
+        return {"pages": [], "slots": [("S", (self.cfg.heads, self.cfg.dim, self.cfg.vdim))]}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T = self.cfg, self.ops, step.T
+        q, k, v, g, a1 = cols
+        z = step.scratch("gla_z", T * c.heads * c.dim)
+        self.a2(step, a1, ld, z.data_ptr(), c.heads * c.dim)
+        o = step.scratch("gla_o", T * self.width)
+        ops.gla_scan(step.b, q, ld, k, ld, v, ld, z.data_ptr(), c.heads * c.dim, c.heads, c.dim, c.vdim, c.dim ** -0.5, c.tau, state["S"], o,
+                     self.width, step.st)
+        ops.headnorm_gate(o.data_ptr(), self.width, g, ld, self.norm_w, c.heads, c.vdim, self.eps, out, self.width, T, step.st)
+
+
+class MixerGroup:
+    """One or more mechanisms reading the same input: their input projections run as one fused product, each mechanism's result goes
+    through its own output projection, and the results are added with the given weights."""
+
+    def __init__(self, members, ops, device):
+        self.members = members                       # [(name, mechanism, weight)]
+        self.ops = ops
+        parts = [p for _, m, _ in members for p in m.inputs]
+        self.proj = FusedLinear(parts, ops, device)
+        self.spans, i = [], 0
+        for _, m, _ in members:
+            self.spans.append(self.proj.offsets[i:i + len(m.inputs)])
+            i += len(m.inputs)
+
+    def state_spec(self):
+        spec = {"pages": [], "slots": []}
+        for name, m, _ in self.members:
+            s = m.state_spec()
+            spec["pages"] += [(f"{name}.{n}", g, wd) for n, g, wd in s["pages"]]
+            spec["slots"] += [(f"{name}.{n}", shape) for n, shape in s["slots"]]
+        return spec
+
+    def forward(self, step, h, state, y):
+        """h [T][d] -> y [T][d]"""
+        T, N = step.T, self.proj.N
+        cols = step.scratch("mix_cols", T * N)
+        self.proj(step, h.data_ptr(), self.proj.K, cols.data_ptr(), N)
+        for i, ((name, m, weight), span) in enumerate(zip(self.members, self.spans)):
+            part = step.scratch("mix_part", T * m.width)
+            sub = {k[len(name) + 1:]: t for k, t in state.items() if k.startswith(name + ".")}
+            m.forward(step, [cols.data_ptr() + o * F32B for o in span], N, sub, part)
+            m.out(step, part.data_ptr(), m.width, y.data_ptr(), m.out.N, alpha=weight, accumulate=i > 0)
+
+
+class PolyNormFeedForward:
+    """Dense feed-forward W_down act(W_up h) with act = a N(z) + b N(z^2) + c N(z^3) + e, N = division of a token's vector by its rms."""
+
+    def __init__(self, w, pre, ops, device, eps):
+        self.ops, self.eps = ops, eps
+        self.up = FusedLinear([(w[pre + "up"], w.get(pre + "up.b"))], ops, device)
+        self.down = FusedLinear([(w[pre + "down"], w.get(pre + "down.b"))], ops, device)
+        self.coef = w[pre + "act"].float().contiguous()
+
+    def state_spec(self):
+        return {"pages": [], "slots": []}
+
+    def forward(self, step, h, state, y):
+        T, n = step.T, self.up.N
+        z = step.scratch("ff_z", T * n)
+        self.up(step, h.data_ptr(), self.up.K, z.data_ptr(), n)
+        self.ops.polynorm(z, n, self.coef, self.eps, z, n, T, n, step.st)
+        self.down(step, z.data_ptr(), n, y.data_ptr(), self.down.N)

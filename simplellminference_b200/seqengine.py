@@ -1,0 +1,278 @@
+"""Step function, cache and state manager for models built from the ragged-token-batch mechanisms (``layers``).
+
+``SequenceEngine`` owns, for every layer run of a model, what that run's mixer declares in ``state_spec``: page pools for softmax
+attention (pages handed out by the same bookkeeping as the batched Llama decoder, ``batch.KvPages``) and slot-indexed fp32 state for the
+recurrent mixers. One ``run`` is one step: any mix of portions of prompts and single decoded tokens, each request at its own position.
+Logits at a position do not depend on how the tokens were cut into steps, on the neighbours in the batch, or on which pages and slot a
+request got, beyond the rounding of differently ordered sums.
+
+``SequenceDecoder`` puts the decoder interface of ``scheduler.ContinuousBatcher`` on top (add / step / tokens / remove / position ...),
+with prompts processed in chunks beside the decoding requests and the device sampler (``sllm_sample_f32``) for the next tokens.
+
+Additive to the reference, which decodes one sequence token by token (source/model/model.cpp:148-185)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib
+from .batch import KvPages
+from .config import BF16
+
+QUERY_TILE = 32      # queries per attention work item (kBQ of csrc/seq_attn.cu)
+KEY_TILE = 32
+
+
+class Step:
+    """What the mechanisms see of one step: sizes, the batch description, the stream, scratch memory."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.T = self.nseg = 0
+        self.b = _lib.SeqBatch()
+        self.st = None
+        self.nsplit = 1
+
+    def scratch(self, name: str, n_floats: int) -> torch.Tensor:
+        return self.engine._scratch(name, n_floats)
+
+    def gemm_scratch(self, K: int, N: int):
+        """bf16 copy of the activations + the plain product, for products that go to the tensor cores (None: too few rows to pay)."""
+        if not self.engine.tensor_cores or self.T < 64:
+            return None
+        n_bytes = ((self.T * K * 2 + 255) // 256) * 256 + self.T * N * 4
+        return self.engine._scratch("gemm", (n_bytes + 3) // 4)
+
+
+class SequenceEngine:
+    def __init__(self, model, max_tokens: int, max_seqs: int = 4, page_len: int = 64, tensor_cores: bool | None = None):
+        if page_len % KEY_TILE:
+            raise ValueError(f"page_len must be a multiple of {KEY_TILE}")
+        self.model, self.ops, self.device = model, model.ops, model.device
+        self.max_seqs, self.page_len = max_seqs, page_len
+        self.n_pages = max(1, -(-max_tokens // page_len))
+        self.max_pages = self.n_pages                       # one request may hold the whole pool
+        self.max_len = self.n_pages * page_len
+        self.pages = KvPages(self.n_pages, page_len, max_seqs, self.max_pages)
+        self.tensor_cores = self.ops.tensor_cores if tensor_cores is None else (tensor_cores and self.ops.w_dtype == BF16)
+        kv_t = torch.bfloat16 if self.ops.kv_dtype == BF16 else torch.float32
+        self.states = []
+        for spec in model.state_specs():
+            st = {}
+            for name, kv_heads, width in spec["pages"]:
+                st[name] = torch.zeros(self.n_pages, kv_heads, page_len, width, dtype=kv_t, device=self.device)
+            for name, shape in spec["slots"]:
+                st[name] = torch.zeros((max_seqs,) + tuple(shape), dtype=torch.float32, device=self.device)
+            self.states.append(st)
+        self._slot_tensors = [t for st, spec in zip(self.states, model.state_specs()) for name, _ in spec["slots"] for t in [st[name]]]
+        self.free_slots = list(range(max_seqs - 1, -1, -1))
+        self.pos = [0] * max_seqs
+        self.live = set()
+        self._bufs = {}
+        self._meta_dev = None
+        self._meta_host = None
+        self._meta_event = None
+        self.step_obj = Step(self)
+        self.steps_run = 0
+
+    # ---- requests ----
+    def admit(self) -> int:
+        """A free state slot for a new request; its recurrent state starts at zero."""
+        if not self.free_slots:
+            raise RuntimeError(f"all {self.max_seqs} state slots are in use")
+        slot = self.free_slots.pop()
+        for t in self._slot_tensors:
+            t[slot].zero_()
+        self.pos[slot] = 0
+        self.live.add(slot)
+        return slot
+
+    def release(self, slot: int) -> None:
+        """Give back the request's pages and its slot."""
+        if slot not in self.live:
+            raise ValueError(f"slot {slot} is not in use")
+        self.pages.release(slot)
+        self.live.discard(slot)
+        self.free_slots.append(slot)
+
+    @property
+    def free_pages(self) -> int:
+        return self.pages.free
+
+    # ---- memory ----
+    def _scratch(self, name: str, n_floats: int) -> torch.Tensor:
+        t = self._bufs.get(name)
+        if t is None or t.numel() < n_floats:
+            t = torch.empty(max(n_floats, 1), dtype=torch.float32, device=self.device)
+            self._bufs[name] = t
+        return t
+
+    def _upload(self, arrays):
+        """The step's index arrays as ONE host-to-device copy; returns their device addresses."""
+        sizes = [a.size for a in arrays]
+        total = sum(sizes)
+        if self._meta_host is None or self._meta_host.numel() < total:
+            cap = max(total, 4096)
+            self._meta_host = torch.empty(cap, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else torch.empty(cap, dtype=torch.int32)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        if self._meta_event is not None:
+            self._meta_event.synchronize()          # the previous step's copy has left the pinned buffer
+        host = self._meta_host.numpy()
+        off, ptrs = 0, []
+        for a, n in zip(arrays, sizes):
+            host[off:off + n] = a.reshape(-1)
+            ptrs.append(self._meta_dev.data_ptr() + 4 * off)
+            off += n
+        self._meta_dev[:total].copy_(self._meta_host[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            self._meta_event = torch.cuda.Event()
+            self._meta_event.record()
+        return ptrs
+
+    # ---- the step ----
+    def run(self, entries, tap=None):
+        """entries: [(slot, tokens, want)] — for each request its next tokens and the indices among them whose logits are asked for.
+        Returns a float32 tensor [sum of wants][vocab] on the device (None if nothing is wanted), rows in the order of entries and want."""
+        entries = [(s, np.ascontiguousarray(t, dtype=np.int32).reshape(-1), list(w)) for s, t, w in entries]
+        entries = [e for e in entries if e[1].size]
+        if not entries:
+            return None
+        if len({s for s, _, _ in entries}) != len(entries):
+            raise ValueError("a request may bring one portion per step")
+        for slot, toks, _ in entries:                     # pages first, all or nothing
+            if slot not in self.live:
+                raise ValueError(f"slot {slot} is not in use")
+        need = sum(max(0, -(-(self.pos[s] + t.size) // self.page_len) - self.pages.held(s)) for s, t, _ in entries)
+        if need > self.pages.free:
+            raise _lib.SllmError(_lib.ENOMEM, f"out of cache pages: this step needs {need} more, {self.pages.free} free")
+        for slot, toks, _ in entries:
+            self.pages.reserve(slot, self.pos[slot] + toks.size)
+        T = sum(t.size for _, t, _ in entries)
+        nseg = len(entries)
+        ids = np.concatenate([t for _, t, _ in entries])
+        tok_slot = np.concatenate([np.full(t.size, s, dtype=np.int32) for s, t, _ in entries])
+        tok_pos = np.concatenate([np.arange(self.pos[s], self.pos[s] + t.size, dtype=np.int32) for s, t, _ in entries])
+        seg_len = np.array([t.size for _, t, _ in entries], dtype=np.int32)
+        seg_start = np.concatenate([[0], np.cumsum(seg_len)[:-1]]).astype(np.int32)
+        seg_slot = np.array([s for s, _, _ in entries], dtype=np.int32)
+        seg_pos0 = np.array([self.pos[s] for s, _, _ in entries], dtype=np.int32)
+        qt_seg, qt_off = [], []
+        for i, n in enumerate(seg_len):
+            for off in range(0, int(n), QUERY_TILE):
+                qt_seg.append(i)
+                qt_off.append(off)
+        # long tiles first: a tile's work grows with its last position
+        order = sorted(range(len(qt_seg)), key=lambda j: -(int(seg_pos0[qt_seg[j]]) + qt_off[j]))
+        qt_seg = np.array([qt_seg[j] for j in order], dtype=np.int32)
+        qt_off = np.array([qt_off[j] for j in order], dtype=np.int32)
+        rows = np.array([int(seg_start[i]) + int(k) for i, (_, t, w) in enumerate(entries) for k in w], dtype=np.int32)
+        for i, (_, t, w) in enumerate(entries):
+            if any(k < 0 or k >= t.size for k in w):
+                raise ValueError("a wanted index lies outside the entry's tokens")
+        table = self.pages.table().astype(np.int32)
+        arrays = [ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, qt_seg, qt_off, rows if rows.size else np.zeros(1, np.int32), table]
+        p = self._upload(arrays)
+        step = self.step_obj
+        step.T, step.nseg = T, nseg
+        b = step.b
+        b.T, b.nseg = T, nseg
+        b.tok_slot, b.tok_pos, b.seg_start, b.seg_len, b.seg_slot, b.seg_pos0 = p[1], p[2], p[3], p[4], p[5], p[6]
+        b.qt_seg, b.qt_off, b.n_qtiles = p[7], p[8], int(qt_seg.size)
+        b.block_table, b.max_pages, b.page_len = p[10], self.max_pages, self.page_len
+        step.st = torch.cuda.current_stream(self.device).cuda_stream
+        # share the key tiles of long contexts among CTAs when the step has few queries (decode): aim at ~2 CTAs per SM
+        key_tiles = max(1, -(-int((seg_pos0 + seg_len).max()) // KEY_TILE))
+        step.nsplit = int(min(key_tiles, max(1, 64 // max(1, int(qt_seg.size)))))
+        ids_t = _PtrView(p[0])
+        rows_t = _PtrView(p[9])
+        logits = self.model.forward(step, ids_t, self.states, rows_t, int(rows.size), tap=tap)
+        for slot, toks, _ in entries:
+            self.pos[slot] += int(toks.size)
+        self.steps_run += 1
+        return logits
+
+
+class _PtrView:
+    """A device address with the one method the launch wrappers use of a tensor."""
+
+    def __init__(self, ptr: int):
+        self._ptr = ptr
+
+    def data_ptr(self) -> int:
+        return self._ptr
+
+
+class SequenceDecoder:
+    """The decoder interface of ``scheduler.ContinuousBatcher`` over a ``SequenceEngine``: every ``step`` feeds each live request either its
+    next portion of the prompt (at most ``prefill_chunk`` tokens) or its last produced token, and draws the next token of every request
+    whose prompt is through. ``tokens(slot)`` follows the convention of the batched Llama decoder: the tokens that FOLLOWED positions
+    0 .. position-1 (the prompt's own continuation first, then what was produced)."""
+
+    def __init__(self, engine: SequenceEngine, prefill_chunk: int = 256):
+        self.engine, self.prefill_chunk = engine, max(1, prefill_chunk)
+        self.max_seqs, self.page_len, self.n_pages, self.max_len = engine.max_seqs, engine.page_len, engine.n_pages, engine.max_len
+        self._req = {}
+        self._idx = torch.zeros(engine.max_seqs, dtype=torch.int32, device=engine.device)
+
+    @property
+    def free_pages(self) -> int:
+        return self.engine.free_pages
+
+    def add(self, prompt) -> int:
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32).reshape(-1)
+        if prompt.size < 1:
+            raise ValueError("empty prompt")
+        slot = self.engine.admit()
+        self._req[slot] = {"prompt": prompt, "fed": 0, "out": [], "limit": None, "sampling": None}
+        return slot
+
+    def set_limit(self, slot: int, positions: int) -> None:
+        """The request stops taking part in steps once it holds this many positions."""
+        self._req[slot]["limit"] = int(positions)
+
+    def set_sampling(self, slot: int, temperature: float = 1.0, top_k: int = 0, top_p: float = 0.0, seed: int = 0) -> None:
+        self._req[slot]["sampling"] = (float(temperature), int(top_k), float(top_p), int(seed))
+
+    def position(self, slot: int) -> int:
+        return self.engine.pos[slot]
+
+    def remove(self, slot: int) -> None:
+        self.engine.release(slot)
+        del self._req[slot]
+
+    def tokens(self, slot: int) -> np.ndarray:
+        r = self._req[slot]
+        return np.concatenate([r["prompt"][1:r["fed"]], np.array(r["out"], dtype=np.int32)]).astype(np.int32)
+
+    def step(self, n: int = 1) -> None:
+        eng = self.engine
+        for _ in range(n):
+            entries, drawing = [], []
+            for slot, r in self._req.items():
+                if r["limit"] is not None and eng.pos[slot] >= r["limit"]:
+                    continue
+                left = r["prompt"].size - r["fed"]
+                if left > 0:
+                    take = min(left, self.prefill_chunk)
+                    toks = r["prompt"][r["fed"]:r["fed"] + take]
+                    r["fed"] += take
+                    last = r["fed"] == r["prompt"].size
+                    entries.append((slot, toks, [take - 1] if last else []))
+                    if last:
+                        drawing.append(slot)
+                else:
+                    entries.append((slot, np.array([r["out"][-1]], dtype=np.int32), [0]))
+                    drawing.append(slot)
+            if not entries:
+                return
+            logits = eng.run(entries)
+            if not drawing:
+                continue
+            st = torch.cuda.current_stream(eng.device).cuda_stream
+            for i, slot in enumerate(drawing):
+                temperature, top_k, top_p, seed = self._req[slot]["sampling"] or (0.0, 0, 0.0, 0)
+                eng.ops.sample(logits.data_ptr() + 4 * i * logits.shape[1], logits.shape[1], temperature, top_k, top_p, seed, eng.pos[slot] - 1,
+                               self._idx.data_ptr() + 4 * i, st)
+            drawn = self._idx[:len(drawing)].cpu().numpy()
+            for i, slot in enumerate(drawing):
+                self._req[slot]["out"].append(int(drawn[i]))

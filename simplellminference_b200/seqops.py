@@ -1,0 +1,88 @@
+"""Python face of the ragged-token-batch launchers (sllm_seq_* of include/sllm_b200.h), in the manner of kernels.py: torch tensors only
+carry device memory, every function enqueues one kernel (or a short fixed sequence) on the stream it is given and returns. There is no
+fallback: the launchers raise if the CUDA library is missing or a call fails.
+
+Additive to the reference (one Llama forward, source/model/model.cpp:40-140): these are the blocks of models that mix softmax attention
+over a paged cache with recurrent layers."""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib
+from .config import BF16, F32
+
+_NULL = None
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+class Ops:
+    """Bound launchers + the numeric mode of a run: ``w_dtype`` is the storage type of the matrices, ``round_a`` rounds activations to bf16
+    as matrix-product operands (the bf16 mode), ``kv_dtype`` the type of the attention pools."""
+
+    def __init__(self, w_dtype: int, build: bool = False):
+        self.lib = _lib.load_seq(build=build)
+        self.w_dtype = w_dtype
+        self.round_a = 1 if w_dtype == BF16 else 0
+        self.kv_dtype = BF16 if w_dtype == BF16 else F32
+        self.tensor_cores = w_dtype == BF16
+        self.launches = 0
+
+    def _ck(self, rc):
+        self.launches += 1
+        if rc != 0:
+            raise _lib.SllmError(rc, self.lib.sllm_last_error().decode(errors="replace"))
+
+    # ---- rows ----
+    def embed(self, ids, table, vocab, d, streams, out, T, st):
+        self._ck(self.lib.sllm_seq_embed(_p(ids), _p(table), self.w_dtype, vocab, d, streams, _p(out), T, st))
+
+    def hyper_read(self, x, streams, T, d, coef, norm_w, groups, eps, y, st):
+        self._ck(self.lib.sllm_seq_hyper_read(_p(x), streams, T, d, _p(coef), _p(norm_w), groups, eps, _p(y), st))
+
+    def hyper_write(self, x, streams, T, d, mix, outc, y, st):
+        self._ck(self.lib.sllm_seq_hyper_write(_p(x), streams, T, d, _p(mix), _p(outc), _p(y), st))
+
+    def linear(self, a_ptr, lda, w, ldw, bias, c_ptr, ldc, T, N, K, st, alpha=1.0, accumulate=False, batch=1, a_bs=0, w_bs=0, bias_bs=0,
+               c_bs=0, scratch=None):
+        self._ck(self.lib.sllm_seq_linear(a_ptr, lda, _p(w), self.w_dtype, ldw, _p(bias), c_ptr, ldc, T, N, K, alpha, int(accumulate),
+                                          self.round_a, batch, a_bs, w_bs, bias_bs, c_bs, _p(scratch) if self.tensor_cores else None, st))
+
+    def polynorm(self, z, ldz, coef, eps, out, ldo, T, n, st):
+        self._ck(self.lib.sllm_seq_polynorm(_p(z), ldz, _p(coef), eps, _p(out), ldo, T, n, st))
+
+    def gather_rows(self, x, ldx, rows, n, d, out, st):
+        self._ck(self.lib.sllm_seq_gather_rows(_p(x), ldx, _p(rows), n, d, _p(out), st))
+
+    def headnorm_gate(self, o_ptr, ldo, g_ptr, ldg, w, heads, dv, eps, out, ldout, T, st):
+        self._ck(self.lib.sllm_seq_headnorm_gate(o_ptr, ldo, g_ptr, ldg, _p(w), heads, dv, eps, _p(out), ldout, T, st))
+
+    # ---- attention over the paged cache ----
+    def rotary_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, freq, n_freq, magnitude, vfreq, layout, k_pool, v_pool, st):
+        self._ck(self.lib.sllm_seq_rotary_kv(C.byref(b), q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, _p(freq), n_freq, magnitude,
+                                             _p(vfreq), layout, _p(k_pool), _p(v_pool), self.kv_dtype, st))
+
+    def attention(self, b, q_ptr, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, st):
+        self._ck(self.lib.sllm_seq_attention(C.byref(b), q_ptr, ldq, heads, kv_heads, dk, dv, scale, _p(k_pool), _p(v_pool), self.kv_dtype, nsplit,
+                                             _p(ws), st))
+
+    def attention_finish(self, b, ws, nsplit, heads, dv, vfreq, layout, gate_ptr, ldg, out, ldo, st):
+        self._ck(self.lib.sllm_seq_attention_finish(C.byref(b), _p(ws), nsplit, heads, dv, _p(vfreq), layout, gate_ptr, ldg, _p(out), ldo, st))
+
+    # ---- recurrences ----
+    def conv(self, b, x_ptr, ldx, channels, taps, w, cb, tail, u, ldu, st):
+        self._ck(self.lib.sllm_seq_conv(C.byref(b), x_ptr, ldx, channels, taps, _p(w), _p(cb), _p(tail), _p(u), ldu, st))
+
+    def rglru_scan(self, b, u, ldu, lr_ptr, li_ptr, ldg, y_ptr, ldy, lam, c, channels, state, x_ptr, ldx, taps, tail, out, ldo, st):
+        self._ck(self.lib.sllm_seq_rglru_scan(C.byref(b), _p(u), ldu, lr_ptr, li_ptr, ldg, y_ptr, ldy, _p(lam), c, channels, _p(state), x_ptr, ldx,
+                                              taps, _p(tail), _p(out), ldo, st))
+
+    def gla_scan(self, b, q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, z_ptr, ldz, heads, dk, dv, qscale, tau, state, o, ldo, st):
+        self._ck(self.lib.sllm_seq_gla_scan(C.byref(b), q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, z_ptr, ldz, heads, dk, dv, qscale, tau, _p(state),
+                                            _p(o), ldo, st))
+
+    # ---- sampling (the op of the one-sequence path: temperature <= 0 = first maximum) ----
+    def sample(self, logits_ptr, n, temperature, top_k, top_p, seed, step, idx_ptr, st):
+        self._ck(self.lib.sllm_sample_f32(logits_ptr, n, temperature, top_k, top_p, seed, step, idx_ptr, st))
