@@ -61,6 +61,10 @@ def parse():
                                                           "microbenchmarks, per-phase timelines); their JSON goes under batch_decode / experiments")
     ap.add_argument("--nccl", action="store_true", help="tensor parallel: NCCL all-reduce instead of the fused peer-memory one")
     ap.add_argument("--kernel-only", default=None, help="profiling aid: loop one fused kernel kind and exit")
+    ap.add_argument("--hybrid", default=None, metavar="SIZES",
+                    help="instead of the headline workload: prefill and decode throughput of the Munazen design (softmax attention + recurrent mixers over the "
+                         "ragged-batch engine) at real layer sizes beside the Llama engine at equal size; comma-separated sizes of "
+                         "simplellminference_b200/bench_hybrid.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"hybrid\": [...]}")
     ap.add_argument("--no-batch", action="store_true", help="(kept for old command lines: the secondary measurements are opt-in now, see --extras)")
     return ap.parse_args()
 
@@ -636,6 +640,19 @@ def main():
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
+    if args.hybrid:
+        import torch
+        from simplellminference_b200 import bench_hybrid
+        torch.cuda.set_device(0)
+        sizes = list(bench_hybrid.SIZES) if args.hybrid == "all" else args.hybrid.split(",")
+        hbm, hbm_src = peaks()
+        tf, tf_src = tensor_peak()
+        real = sys.stdout
+        sys.stdout = sys.stderr                      # the per-size lines are progress; the contract is ONE line on stdout
+        res = bench_hybrid.main(sizes, hbm, tf)
+        sys.stdout = real
+        print(json.dumps({"hybrid": res, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf, "bf16_source": tf_src}}))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -409,6 +409,7 @@ typedef struct {
     int32_t n_qtiles;            /* attention work list: tiles of up to 32 consecutive queries of one segment */
     const int32_t* qt_seg;       /* [n_qtiles] segment of the tile */
     const int32_t* qt_off;       /* [n_qtiles] offset of its first query inside the segment */
+    const int32_t* seg_tile0;    /* [nseg] running count of tiles of the segments before this one (tile ids in segment order) */
 } sllm_seq_batch;
 
 /* out[s][t][:] = table[ids[t]][:] for every stream s (a model with one residual stream passes streams = 1) */
@@ -457,15 +458,18 @@ int sllm_seq_conv(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t 
                   const float* tail, float* u, int32_t ldu, sllm_stream_t stream);
 /* Real-gated linear recurrent unit: r = sigmoid(lr), i = sigmoid(li), log a = -c * r * softplus(lam), S <- a*S + sqrt(1 - a^2) * i * u,
  * out = S * gelu_tanh(ypre). state: [slots][channels] fp32, read and written. Also moves the convolution tail on: tail[slot] <- the
- * last taps-1 rows of (tail[slot] ++ xconv rows of the segment) (xconv NULL = no tail). */
+ * last taps-1 rows of (tail[slot] ++ xconv rows of the segment) (xconv NULL = no tail). scratch (NULL = always token by token): 2 * n_qtiles *
+ * channels doubles; with it, steps that hold a portion longer than 32 tokens run as three passes over tiles (tile summaries, carry, outputs). */
 int sllm_seq_rglru_scan(const sllm_seq_batch* b, const float* u, int32_t ldu, const float* lr, const float* li, int32_t ldg,
                         const float* ypre, int32_t ldy, const float* lam, float c, int32_t channels, float* state, const float* xconv,
-                        int32_t ldx, int32_t taps, float* tail, float* out, int32_t ldo, sllm_stream_t stream);
+                        int32_t ldx, int32_t taps, float* tail, float* out, int32_t ldo, void* scratch, sllm_stream_t stream);
 /* Gated linear attention, token by token per head: alpha = sigmoid(z)^(1/tau) per key channel, S <- diag(alpha) S + k v^T (S: dk x dv),
- * o = S^T (q * qscale). state: [slots][heads][dk][dv] fp32, read and written. */
+ * o = S^T (q * qscale). state: [slots][heads][dk][dv] fp32, read and written. dk/32 (rounded up) * dv (rounded up to 32) <= 1024.
+ * scratch (NULL = always token by token): n_qtiles * heads * dk (rounded up to 64) + n_qtiles * heads * dk * dv floats, for the
+ * three-pass form of steps that hold a portion longer than 32 tokens. */
 int sllm_seq_gla_scan(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv,
                       const float* z, int32_t ldz, int32_t heads, int32_t dk, int32_t dv, float qscale, float tau, float* state, float* o,
-                      int32_t ldo, sllm_stream_t stream);
+                      int32_t ldo, void* scratch, sllm_stream_t stream);
 /* out[t][h*dv + j] = o[t][h*dv + j] / sqrt(mean_j(o^2) + eps) * w[j] * silu(g[t][h*dv + j]) */
 int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t ldg, const float* w, int32_t heads, int32_t dv, float eps,
                            float* out, int32_t ldout, int32_t T, sllm_stream_t stream);

@@ -120,7 +120,7 @@ SIGNATURES = {
 class SeqBatch(C.Structure):
     """sllm_seq_batch: one step's ragged token batch (device pointers to its index arrays)."""
     _fields_ = [("T", _I), ("nseg", _I), ("tok_slot", _P), ("tok_pos", _P), ("seg_start", _P), ("seg_len", _P), ("seg_slot", _P),
-                ("seg_pos0", _P), ("block_table", _P), ("max_pages", _I), ("page_len", _I), ("n_qtiles", _I), ("qt_seg", _P), ("qt_off", _P)]
+                ("seg_pos0", _P), ("block_table", _P), ("max_pages", _I), ("page_len", _I), ("n_qtiles", _I), ("qt_seg", _P), ("qt_off", _P), ("seg_tile0", _P)]
 
 
 _B = C.POINTER(SeqBatch)
@@ -135,8 +135,8 @@ SIGNATURES.update({
     "sllm_seq_attention": (C.c_int, [_B, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _P, _P]),
     "sllm_seq_attention_finish": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _P, _I, _P, _I, _P]),
     "sllm_seq_conv": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
-    "sllm_seq_rglru_scan": (C.c_int, [_B, _P, _I, _P, _P, _I, _P, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _I, _P]),
-    "sllm_seq_gla_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P]),
+    "sllm_seq_rglru_scan": (C.c_int, [_B, _P, _I, _P, _P, _I, _P, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _I, _P, _P]),
+    "sllm_seq_gla_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _P]),
     "sllm_seq_headnorm_gate": (C.c_int, [_P, _I, _P, _I, _P, _I, _I, _F, _P, _I, _I, _P]),
 })
 

@@ -66,13 +66,34 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
         const int valid = min(kBK, last_pos + 1 - j0);   // keys of this tile that exist
         __syncthreads();
         const size_t krow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dv);
-        for (int i = threadIdx.x; i < kBK * dkp; i += blockDim.x) {
-            const int r = i / dkp, c = i % dkp;
-            sk[i] = (r < valid && c < dk) ? seq_ld(kp, krow + (size_t)r * dk + c) : 0.0f;
-        }
-        for (int i = threadIdx.x; i < kBK * dv; i += blockDim.x) {
-            const int r = i / dv;
-            sv[i] = r < valid ? seq_ld(vp, vrow + i) : 0.0f;
+        constexpr int E = 16 / sizeof(KV);   // elements per 16-byte load
+        if (dk % E == 0 && dv % E == 0) {
+            // the tile's rows are consecutive in the pool: 16-byte loads, rows beyond `valid` zero-filled (dk is a multiple of 4 here, so the
+            // padding columns of a row are never read)
+            const int kgroups = dk / E, vgroups = dv / E;
+            for (int i = threadIdx.x; i < kBK * kgroups; i += blockDim.x) {
+                const int r = i / kgroups, c = (i % kgroups) * E;
+                float vals[E];
+                seq_ld16(kp + krow + (size_t)r * dk + c, r < valid, vals);
+#pragma unroll
+                for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(sk + r * dkp + c + e) = make_float4(vals[e], vals[e + 1], vals[e + 2], vals[e + 3]);
+            }
+            for (int i = threadIdx.x; i < kBK * vgroups; i += blockDim.x) {
+                const int r = i / vgroups;
+                float vals[E];
+                seq_ld16(vp + vrow + (size_t)i * E, r < valid, vals);
+#pragma unroll
+                for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(sv + (size_t)i * E + e) = make_float4(vals[e], vals[e + 1], vals[e + 2], vals[e + 3]);
+            }
+        } else {
+            for (int i = threadIdx.x; i < kBK * dkp; i += blockDim.x) {
+                const int r = i / dkp, c = i % dkp;
+                sk[i] = (r < valid && c < dk) ? seq_ld(kp, krow + (size_t)r * dk + c) : 0.0f;
+            }
+            for (int i = threadIdx.x; i < kBK * dv; i += blockDim.x) {
+                const int r = i / dv;
+                sv[i] = r < valid ? seq_ld(vp, vrow + i) : 0.0f;
+            }
         }
         __syncthreads();
         // scores: lane = key j0 + lane, four queries of this warp

@@ -15,6 +15,16 @@ __device__ __forceinline__ float seq_ldw(const void* p, int dtype, size_t i) {
 }
 __device__ __forceinline__ float seq_ld(const float* p, size_t i) { return p[i]; }
 __device__ __forceinline__ float seq_ld(const uint16_t* p, size_t i) { return __uint_as_float((uint32_t)p[i] << 16); }
+// 16 bytes of a pool as floats (4 fp32 or 8 bf16 values); `take` false = zeros without touching memory
+__device__ __forceinline__ void seq_ld16(const float* p, bool take, float (&out)[4]) {
+    const float4 v = take ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void seq_ld16(const uint16_t* p, bool take, float (&out)[8]) {
+    const uint4 v = take ? *reinterpret_cast<const uint4*>(p) : make_uint4(0u, 0u, 0u, 0u);
+    out[0] = bf16_lo(v.x); out[1] = bf16_hi(v.x); out[2] = bf16_lo(v.y); out[3] = bf16_hi(v.y);
+    out[4] = bf16_lo(v.z); out[5] = bf16_hi(v.z); out[6] = bf16_lo(v.w); out[7] = bf16_hi(v.w);
+}
 __device__ __forceinline__ void seq_st(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void seq_st(uint16_t* p, size_t i, float v) { p[i] = f32_to_bf16_bits(v); }
 __device__ __forceinline__ float seq_round_bf16(float v) { return __uint_as_float((uint32_t)f32_to_bf16_bits(v) << 16); }

@@ -121,8 +121,10 @@ class GatedLinearRecurrence:
         for which in range(2):   # block-diagonal products: one launch per gate, the blocks as its batch
             ops.linear(u.data_ptr(), W, self.gates_w[which], bs, self.gates_b[which], gates.data_ptr() + which * T * W * F32B, W, T, bs, bs, step.st,
                        batch=c.blocks, a_bs=bs, w_bs=bs * bs, bias_bs=bs, c_bs=bs)
+        tiles = step.b.n_qtiles
+        scan_ws = step.scratch("rg_tiles", 4 * tiles * W) if tiles > step.nseg else None      # (P, Q) per tile and channel, doubles
         ops.rglru_scan(step.b, u, W, gates.data_ptr(), gates.data_ptr() + T * W * F32B, W, y, ld, self.lam, self.decay_scale, W, state["S"],
-                       x, ld, c.conv, tail, out, W, step.st)
+                       x, ld, c.conv, tail, out, W, scan_ws, step.st)
 
 
 class GatedLinearAttention:
@@ -147,8 +149,12 @@ class GatedLinearAttention:
         z = step.scratch("gla_z", T * c.heads * c.dim)
         self.a2(step, a1, ld, z.data_ptr(), c.heads * c.dim)
         o = step.scratch("gla_o", T * self.width)
+        tiles = step.b.n_qtiles
+        scan_ws = None
+        if tiles > step.nseg:                    # a portion longer than one tile: per tile the decay products and the tile's state
+            scan_ws = step.scratch("gla_tiles", (tiles * c.heads * c.dim + 63) // 64 * 64 + tiles * c.heads * c.dim * c.vdim)
         ops.gla_scan(step.b, q, ld, k, ld, v, ld, z.data_ptr(), c.heads * c.dim, c.heads, c.dim, c.vdim, c.dim ** -0.5, c.tau, state["S"], o,
-                     self.width, step.st)
+                     self.width, scan_ws, step.st)
         ops.headnorm_gate(o.data_ptr(), self.width, g, ld, self.norm_w, c.heads, c.vdim, self.eps, out, self.width, T, step.st)
 
 

@@ -41,8 +41,8 @@ class SchedulerStats:
 
 
 class ContinuousBatcher:
-    """``decoder``: a ``BatchDecoder`` (or anything with its add / step / tokens / remove / position / free_pages /
-    max_seqs / page_len / n_pages / max_len interface). Not thread-safe: one host thread drives a decoder, like the reference's model."""
+    """``decoder``: a ``BatchDecoder``, a ``seqengine.SequenceDecoder`` (models of the registry: prompts in portions beside decoding
+    requests) or anything with their add / step / tokens / remove / position / free_pages / max_seqs / page_len / n_pages / max_len interface. Not thread-safe: one host thread drives a decoder, like the reference's model."""
 
     def __init__(self, decoder, eos_id: int | None = None, chunk: int = 8):
         if chunk < 1:
@@ -96,6 +96,10 @@ class ContinuousBatcher:
                 return                                   # FIFO: the head waits, nobody overtakes it
             self.waiting.popleft()
             r.slot = self.dec.add(r.prompt)
+            if hasattr(self.dec, "set_limit"):
+                # a decoder that takes a prompt in portions (seqengine.SequenceDecoder) moves a request by more than one position per step:
+                # tell it where this request ends so that the rest of a chunk of steps leaves it alone
+                self.dec.set_limit(r.slot, r.total)
             if r.sampling:
                 self.dec.set_sampling(r.slot, **r.sampling)
             self.live[r.slot] = r
@@ -115,7 +119,7 @@ class ContinuousBatcher:
             if self.waiting:   # cannot happen with submit()'s check and an empty decoder; guard against a foreign decoder state
                 raise RuntimeError("requests are waiting but none can be admitted into an empty decoder")
             return False
-        n = min([self.chunk] + [r.total - self.dec.position(r.slot) for r in self.live.values()])
+        n = max(1, min([self.chunk] + [r.total - self.dec.position(r.slot) for r in self.live.values()]))
         self.dec.step(n)
         self.stats.steps += n
         self.stats.slot_steps += n * len(self.live)

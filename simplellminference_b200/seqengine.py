@@ -45,7 +45,7 @@ class Step:
 
 
 class SequenceEngine:
-    def __init__(self, model, max_tokens: int, max_seqs: int = 4, page_len: int = 64, tensor_cores: bool | None = None):
+    def __init__(self, model, max_tokens: int, max_seqs: int = 4, page_len: int = 64, tensor_cores: bool | None = None, graphs: bool = True):
         if page_len % KEY_TILE:
             raise ValueError(f"page_len must be a multiple of {KEY_TILE}")
         self.model, self.ops, self.device = model, model.ops, model.device
@@ -74,6 +74,12 @@ class SequenceEngine:
         self._meta_event = None
         self.step_obj = Step(self)
         self.steps_run = 0
+        # Steps of single tokens (decoding) are launch-bound: their kernel sequence depends only on how many requests step and how many
+        # rows of logits are asked for (tokens, positions, slots and the block table are device memory), so it is captured once per such
+        # pair as a CUDA graph and replayed. The first step of a kind runs directly (it sizes the scratch buffers), the second is captured.
+        self.graphs = graphs and self.device.type == "cuda"
+        self._graphs = {}
+        self.graph_replays = 0
 
     # ---- requests ----
     def admit(self) -> int:
@@ -105,6 +111,7 @@ class SequenceEngine:
         if t is None or t.numel() < n_floats:
             t = torch.empty(max(n_floats, 1), dtype=torch.float32, device=self.device)
             self._bufs[name] = t
+            self._graphs = {}          # captured steps hold the old address
         return t
 
     def _upload(self, arrays):
@@ -112,7 +119,9 @@ class SequenceEngine:
         sizes = [a.size for a in arrays]
         total = sum(sizes)
         if self._meta_host is None or self._meta_host.numel() < total:
-            cap = max(total, 4096)
+            # sized once for the largest step the pool can hold, so that the addresses captured in graphs stay valid
+            cap = max(total, 5 * self.max_len + 16 * self.max_seqs + self.max_seqs * self.max_pages + 64)
+            self._graphs = {}
             self._meta_host = torch.empty(cap, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else torch.empty(cap, dtype=torch.int32)
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         if self._meta_event is not None:
@@ -156,6 +165,7 @@ class SequenceEngine:
         seg_start = np.concatenate([[0], np.cumsum(seg_len)[:-1]]).astype(np.int32)
         seg_slot = np.array([s for s, _, _ in entries], dtype=np.int32)
         seg_pos0 = np.array([self.pos[s] for s, _, _ in entries], dtype=np.int32)
+        seg_tile0 = np.concatenate([[0], np.cumsum(-(-seg_len // QUERY_TILE))[:-1]]).astype(np.int32)
         qt_seg, qt_off = [], []
         for i, n in enumerate(seg_len):
             for off in range(0, int(n), QUERY_TILE):
@@ -170,7 +180,7 @@ class SequenceEngine:
             if any(k < 0 or k >= t.size for k in w):
                 raise ValueError("a wanted index lies outside the entry's tokens")
         table = self.pages.table().astype(np.int32)
-        arrays = [ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, qt_seg, qt_off, rows if rows.size else np.zeros(1, np.int32), table]
+        arrays = [ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, qt_seg, qt_off, rows if rows.size else np.zeros(1, np.int32), table, seg_tile0]
         p = self._upload(arrays)
         step = self.step_obj
         step.T, step.nseg = T, nseg
@@ -179,13 +189,38 @@ class SequenceEngine:
         b.tok_slot, b.tok_pos, b.seg_start, b.seg_len, b.seg_slot, b.seg_pos0 = p[1], p[2], p[3], p[4], p[5], p[6]
         b.qt_seg, b.qt_off, b.n_qtiles = p[7], p[8], int(qt_seg.size)
         b.block_table, b.max_pages, b.page_len = p[10], self.max_pages, self.page_len
-        step.st = torch.cuda.current_stream(self.device).cuda_stream
-        # share the key tiles of long contexts among CTAs when the step has few queries (decode): aim at ~2 CTAs per SM
-        key_tiles = max(1, -(-int((seg_pos0 + seg_len).max()) // KEY_TILE))
-        step.nsplit = int(min(key_tiles, max(1, 64 // max(1, int(qt_seg.size)))))
+        b.seg_tile0 = p[11]
         ids_t = _PtrView(p[0])
         rows_t = _PtrView(p[9])
-        logits = self.model.forward(step, ids_t, self.states, rows_t, int(rows.size), tap=tap)
+        n_rows = int(rows.size)
+        decode_only = T == nseg
+        if decode_only:
+            # a fixed share count per batch size keeps the launch sequence of a decoding step independent of the context lengths
+            step.nsplit = max(1, 32 // nseg)
+        else:
+            # share the key tiles of long contexts among CTAs when the step has few query tiles
+            key_tiles = max(1, -(-int((seg_pos0 + seg_len).max()) // KEY_TILE))
+            step.nsplit = int(min(key_tiles, max(1, 64 // max(1, int(qt_seg.size)))))
+        key = (nseg, n_rows)
+        if decode_only and self.graphs and tap is None and key in self._graphs:
+            entry = self._graphs[key]
+            if entry is None:                               # second step of this kind: capture it (a capture does not execute)
+                meta_addr = self._meta_dev.data_ptr()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    step.st = torch.cuda.current_stream(self.device).cuda_stream
+                    out = self.model.forward(step, ids_t, self.states, rows_t, n_rows)
+                entry = self._graphs[key] = (g, out, meta_addr, p[0], p[9])
+            g, logits, meta_addr, ids_addr, rows_addr = entry
+            if meta_addr != self._meta_dev.data_ptr() or ids_addr != p[0] or rows_addr != p[9]:
+                raise RuntimeError("the step's index arrays moved under a captured graph")
+            g.replay()
+            self.graph_replays += 1
+        else:
+            if decode_only and self.graphs and tap is None:
+                self._graphs[key] = None                    # seen once: capture at the next one
+            step.st = torch.cuda.current_stream(self.device).cuda_stream
+            logits = self.model.forward(step, ids_t, self.states, rows_t, n_rows, tap=tap)
         for slot, toks, _ in entries:
             self.pos[slot] += int(toks.size)
         self.steps_run += 1

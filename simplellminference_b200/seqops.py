@@ -75,13 +75,13 @@ class Ops:
     def conv(self, b, x_ptr, ldx, channels, taps, w, cb, tail, u, ldu, st):
         self._ck(self.lib.sllm_seq_conv(C.byref(b), x_ptr, ldx, channels, taps, _p(w), _p(cb), _p(tail), _p(u), ldu, st))
 
-    def rglru_scan(self, b, u, ldu, lr_ptr, li_ptr, ldg, y_ptr, ldy, lam, c, channels, state, x_ptr, ldx, taps, tail, out, ldo, st):
+    def rglru_scan(self, b, u, ldu, lr_ptr, li_ptr, ldg, y_ptr, ldy, lam, c, channels, state, x_ptr, ldx, taps, tail, out, ldo, scratch, st):
         self._ck(self.lib.sllm_seq_rglru_scan(C.byref(b), _p(u), ldu, lr_ptr, li_ptr, ldg, y_ptr, ldy, _p(lam), c, channels, _p(state), x_ptr, ldx,
-                                              taps, _p(tail), _p(out), ldo, st))
+                                              taps, _p(tail), _p(out), ldo, _p(scratch), st))
 
-    def gla_scan(self, b, q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, z_ptr, ldz, heads, dk, dv, qscale, tau, state, o, ldo, st):
+    def gla_scan(self, b, q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, z_ptr, ldz, heads, dk, dv, qscale, tau, state, o, ldo, scratch, st):
         self._ck(self.lib.sllm_seq_gla_scan(C.byref(b), q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, z_ptr, ldz, heads, dk, dv, qscale, tau, _p(state),
-                                            _p(o), ldo, st))
+                                            _p(o), ldo, _p(scratch), st))
 
     # ---- sampling (the op of the one-sequence path: temperature <= 0 = first maximum) ----
     def sample(self, logits_ptr, n, temperature, top_k, top_p, seed, step, idx_ptr, st):
