@@ -58,7 +58,8 @@ int sllm_abi_version(void);
  * a time when 3 or more sequences share a launch, key 7 (with key 6) = down projection with K cut in two over grid.y when more sequences
  * are live than whole rows fit shared memory, so that Wdown is read once (all 0 by default: experimental until measured); key 8 = decode
  * megakernel MEASUREMENT aid, results are garbage: bit 0 = skip the grid barriers, bit 1 = skip the dot products (tools/mega_debug.py),
- * bit 4 = tensor-parallel prefill without its peer-memory exchanges (the GEMM / attention time alone) */
+ * bit 4 = tensor-parallel prefill without its peer-memory exchanges (the GEMM / attention time alone); key 9 = ragged-batch attention
+ * (sllm_seq_attention): 1 (default) tensor-core body for bf16 pools on steps that hold a prompt portion, 0 = always the fp32 body */
 int sllm_tune(int32_t key, int32_t value);
 /* device facts the host side sizes things by: sm count, max opt-in shared memory per block, total/free HBM */
 int sllm_device_info(int32_t* sm_count, int32_t* smem_optin_bytes, size_t* hbm_total, size_t* hbm_free);

@@ -12,6 +12,8 @@
 
 namespace sllm {
 
+extern int g_tune_seq_attn_mma;   // runtime.cu: 1 (default) = tensor-core attention body where it applies, 0 = always the fp32 body
+
 // cos and sin of pos * freq. The product is formed and reduced in double: at position 1000 an fp32 product is already off by up to
 // 3e-5 rad, five hundred times the rounding of everything else in the layer, and the error would grow with the position.
 __device__ __forceinline__ void seq_angle(int pos, double freq, float* sn, float* cs) {
@@ -152,6 +154,181 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
         for (int c = 0; c < kMaxDvChunks; ++c) {
             const int col = c * 32 + lane;
             if (col < dv) rec[2 + col] = acc[i][c];
+        }
+    }
+}
+
+
+// ---- tensor-core body for bf16 pools (the bf16 mode) ------------------------------------------------------------------------------------
+// CTA = (tile of up to 32 queries, head, share of the key tiles), two warps of 16 queries each. Scores = Q K^T with mma.sync m16n8k16
+// (q rounded to bf16 as it is loaded, keys as cached, fp32 accumulation); the softmax runs on the accumulator fragments in fp32 (row
+// maxima across the four lanes of a quad); the weights enter the second product as TWO bf16 terms (p = hi + lo, |p - hi - lo| < 2^-17 p),
+// so that P V keeps the weights to fp32 working accuracy while the values come from the cache as they are. A fragment of S maps
+// register-for-register onto an A fragment of P. K is staged row-major (rows padded by 16 bytes), V transposed ([dv][keys], same
+// padding): both make the 32-bit B-fragment loads conflict-free. Writes the same (max, sum, unnormalised output) records as the fp32 body.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16); }
+// p = hi + lo with both terms bf16: hi = round(p), lo = round(p - hi)
+__device__ __forceinline__ void split_bf16(float p0, float p1, uint32_t* hi, uint32_t* lo) {
+    const uint16_t h0 = f32_to_bf16_bits(p0), h1 = f32_to_bf16_bits(p1);
+    *hi = (uint32_t)h0 | ((uint32_t)h1 << 16);
+    *lo = pack_bf16(p0 - __uint_as_float((uint32_t)h0 << 16), p1 - __uint_as_float((uint32_t)h1 << 16));
+}
+
+constexpr int kMmaDkSteps = 8, kMmaDvTiles = 16;   // dk <= 128 (multiple of 16), dv <= 128 (multiple of 8)
+
+__global__ void __launch_bounds__(64) seq_attention_mma_kernel(AttnArgs p) {
+    extern __shared__ __align__(16) uint16_t smh[];
+    const int dk = p.dk, dv = p.dv, ldk = dk + 8, ldv = kBK + 8;
+    uint16_t* sK = smh;               // [kBK][ldk]
+    uint16_t* sVt = sK + kBK * ldk;   // [dv][ldv]
+    const sllm_seq_batch& b = p.b;
+    const int qt = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    const int seg = b.qt_seg[qt], off = b.qt_off[qt];
+    const int nq = min(kBQ, b.seg_len[seg] - off), t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
+    const int gkv = h / (p.heads / p.kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int dks = dk / 16, dvt = dv / 8;
+    const uint16_t* kp = reinterpret_cast<const uint16_t*>(p.k_pool);
+    const uint16_t* vp = reinterpret_cast<const uint16_t*>(p.v_pool);
+    const int r0 = warp * 16 + g, r1 = r0 + 8;           // this thread's two query rows inside the tile
+    const bool ok0 = r0 < nq, ok1 = r1 < nq;
+    uint32_t qf[kMmaDkSteps][4];
+#pragma unroll
+    for (int ks = 0; ks < kMmaDkSteps; ++ks) {
+        if (ks < dks) {
+            const float* q0 = p.q + (size_t)(t0 + r0) * p.ldq + (size_t)h * dk + ks * 16 + 2 * c;
+            const float* q1 = p.q + (size_t)(t0 + r1) * p.ldq + (size_t)h * dk + ks * 16 + 2 * c;
+            qf[ks][0] = ok0 ? pack_bf16(q0[0], q0[1]) : 0u;
+            qf[ks][1] = ok1 ? pack_bf16(q1[0], q1[1]) : 0u;
+            qf[ks][2] = ok0 ? pack_bf16(q0[8], q0[9]) : 0u;
+            qf[ks][3] = ok1 ? pack_bf16(q1[8], q1[9]) : 0u;
+        } else {
+            qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
+        }
+    }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // l: this thread's share of the row sums (added over the quad at the end)
+    float o[kMmaDvTiles][4];
+#pragma unroll
+    for (int nt = 0; nt < kMmaDvTiles; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+    const int last_pos = pos0 + nq - 1, nkt = last_pos / kBK + 1;
+    const int warp_last = pos0 + min(nq - 1, warp * 16 + 15);
+    const bool warp_live = warp * 16 < nq;
+    for (int kt = split; kt < nkt; kt += p.nsplit) {
+        const int j0 = kt * kBK;
+        const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
+        const int valid = min(kBK, last_pos + 1 - j0);
+        const size_t krow = seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dv);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kBK * (dk / 8); i += blockDim.x) {
+            const int r = i / (dk / 8), cc = (i % (dk / 8)) * 8;
+            const uint4 v = r < valid ? *reinterpret_cast<const uint4*>(kp + krow + (size_t)r * dk + cc) : make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(sK + r * ldk + cc) = v;
+        }
+        for (int i = threadIdx.x; i < kBK * (dv / 8); i += blockDim.x) {
+            const int r = i % kBK, cc = (i / kBK) * 8;     // consecutive threads take consecutive keys: the transposed stores spread over the banks
+            const uint4 v = r < valid ? *reinterpret_cast<const uint4*>(vp + vrow + (size_t)r * dv + cc) : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                sVt[(cc + 2 * e) * ldv + r] = (uint16_t)(w[e] & 0xffffu);
+                sVt[(cc + 2 * e + 1) * ldv + r] = (uint16_t)(w[e] >> 16);
+            }
+        }
+        __syncthreads();
+        if (!warp_live || j0 > warp_last) continue;
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < kMmaDkSteps; ++ks) {
+            if (ks < dks) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const uint16_t* kr = sK + (nt * 8 + g) * ldk + ks * 16 + 2 * c;
+                    mma_bf16_16816(s[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+                }
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = j0 + nt * 8 + 2 * c + (e & 1);
+                const bool see = (e < 2) ? (ok0 && key <= pos0 + r0) : (ok1 && key <= pos0 + r1);
+                s[nt][e] = see ? s[nt][e] * p.scale : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float corr0 = (mn0 == -INFINITY) ? 1.0f : expf(m0 - mn0), corr1 = (mn1 == -INFINITY) ? 1.0f : expf(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        l0 *= corr0;
+        l1 *= corr1;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            s[nt][0] = s[nt][0] == -INFINITY ? 0.0f : expf(s[nt][0] - mn0);
+            s[nt][1] = s[nt][1] == -INFINITY ? 0.0f : expf(s[nt][1] - mn0);
+            s[nt][2] = s[nt][2] == -INFINITY ? 0.0f : expf(s[nt][2] - mn1);
+            s[nt][3] = s[nt][3] == -INFINITY ? 0.0f : expf(s[nt][3] - mn1);
+            l0 += s[nt][0] + s[nt][1];
+            l1 += s[nt][2] + s[nt][3];
+        }
+#pragma unroll
+        for (int nt = 0; nt < kMmaDvTiles; ++nt) {
+            o[nt][0] *= corr0;
+            o[nt][1] *= corr0;
+            o[nt][2] *= corr1;
+            o[nt][3] *= corr1;
+        }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {           // 32 keys = two k-steps of 16; S tiles 2ks and 2ks+1 are the A fragment's halves
+            uint32_t ah[4], al[4];
+            split_bf16(s[2 * ks][0], s[2 * ks][1], &ah[0], &al[0]);
+            split_bf16(s[2 * ks][2], s[2 * ks][3], &ah[1], &al[1]);
+            split_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1], &ah[2], &al[2]);
+            split_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3], &ah[3], &al[3]);
+#pragma unroll
+            for (int nt = 0; nt < kMmaDvTiles; ++nt) {
+                if (nt < dvt) {
+                    const uint16_t* vr = sVt + (nt * 8 + g) * ldv + ks * 16 + 2 * c;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vr), b1 = *reinterpret_cast<const uint32_t*>(vr + 8);
+                    mma_bf16_16816(o[nt], ah, b0, b1);
+                    mma_bf16_16816(o[nt], al, b0, b1);
+                }
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = half ? r1 : r0;
+        if (r >= nq) continue;
+        float* rec = p.ws + (((size_t)(t0 + r) * p.heads + h) * p.nsplit + split) * (dv + 2);
+        if (c == 0) {
+            rec[0] = half ? m1 : m0;
+            rec[1] = half ? l1 : l0;
+        }
+#pragma unroll
+        for (int nt = 0; nt < kMmaDvTiles; ++nt) {
+            if (nt < dvt) {
+                rec[2 + nt * 8 + 2 * c] = o[nt][2 * half];
+                rec[2 + nt * 8 + 2 * c + 1] = o[nt][2 * half + 1];
+            }
         }
     }
 }
@@ -297,6 +474,14 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes(), SLLM_ENOTSUP, "seq_attention: heads of %d + %d floats need %zu bytes of shared memory", dk, dv, smem);
     AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws};
     dim3 grid(b->n_qtiles, heads, nsplit);
+    // steps that hold a portion of a prompt, bf16 pools, head widths the fragments take: the tensor-core body
+    if (kv_dtype == SLLM_BF16 && b->T > b->nseg && dk % 16 == 0 && dk <= 16 * kMmaDkSteps && dv % 8 == 0 && dv <= 8 * kMmaDvTiles && g_tune_seq_attn_mma) {
+        const size_t smem_mma = ((size_t)kBK * (dk + 8) + (size_t)dv * (kBK + 8)) * sizeof(uint16_t);
+        seq_attention_mma_kernel<<<grid, 64, smem_mma, as_stream(stream)>>>(p);
+        ++g_launches;
+        SLLM_LAUNCH_CHECK();
+        return SLLM_OK;
+    }
     if (kv_dtype == SLLM_F32) {
         if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         seq_attention_kernel<float><<<grid, 256, smem, as_stream(stream)>>>(p);

@@ -4,7 +4,8 @@
 //   * tile_kernel  (any shape): 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMAs with fp32 accumulation. This is
 //     the body of the all-fp32 mode, and of bf16 products whose shape the tensor-core tiles do not take;
 //   * the tcgen05 GEMM of the prefill path (prefill_gemm.cu) for bf16 weights when the caller passes a bf16 scratch for A and the shape
-//     fits its TMA boxes; bias, alpha and accumulation then run as a short epilogue kernel over C.
+//     fits its TMA boxes; without bias and scale the GEMM's own epilogue stores (or adds) into C, otherwise bias, alpha and accumulation
+//     run as a short epilogue kernel over C.
 // In bf16 mode (round_a) the activations are rounded to bf16 as they are loaded, so all three bodies multiply the same operands and
 // differ only in summation order.
 #include "prefill.cuh"
@@ -216,9 +217,15 @@ extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32
         seq_to_bf16_kernel<<<(int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8), 256, 0, st>>>(A, lda, reinterpret_cast<uint16_t*>(a16), T, K);
         ++g_launches;
         SLLM_LAUNCH_CHECK();
-        float* P = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + (((size_t)T * K * 2 + 255) / 256) * 256);   // product scratch behind the bf16 rows
         PfGemmArgs a{};
-        a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.epilogue = PF_EPI_STORE; a.out = P; a.ld_out = N; a.n_valid = N; a.bn = 0;
+        a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.bn = 0; a.n_valid = N;
+        if (!bias && alpha == 1.0f && ((uintptr_t)C % 16) == 0) {
+            // nothing to do after the product: the GEMM's own epilogue stores (or adds) straight into C
+            a.epilogue = accumulate ? PF_EPI_RESID : PF_EPI_STORE; a.out = C; a.ld_out = ldc;
+            return pf_gemm(cache, a, st);
+        }
+        float* P = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + (((size_t)T * K * 2 + 255) / 256) * 256);   // product scratch behind the bf16 rows
+        a.epilogue = PF_EPI_STORE; a.out = P; a.ld_out = N;
         const int rc = pf_gemm(cache, a, st);
         if (rc != SLLM_OK) return rc;
         const size_t m = (size_t)T * N;
