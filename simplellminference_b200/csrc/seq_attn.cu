@@ -164,8 +164,9 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
 // (q rounded to bf16 as it is loaded, keys as cached, fp32 accumulation); the softmax runs on the accumulator fragments in fp32 (row
 // maxima across the four lanes of a quad); the weights enter the second product as TWO bf16 terms (p = hi + lo, |p - hi - lo| < 2^-17 p),
 // so that P V keeps the weights to fp32 working accuracy while the values come from the cache as they are. A fragment of S maps
-// register-for-register onto an A fragment of P. K is staged row-major (rows padded by 16 bytes), V transposed ([dv][keys], same
-// padding): both make the 32-bit B-fragment loads conflict-free. Writes the same (max, sum, unnormalised output) records as the fp32 body.
+// register-for-register onto an A fragment of P. K and V tiles are staged row-major as cached (rows padded by 16 bytes: conflict-free
+// fragment loads; V's B fragments come out of ldmatrix.trans) by cp.async into two stages, the next tile in flight while this one is
+// multiplied; four warps = two query heads of one kv head share a staged tile when the group size is even. Writes the same (max, sum, unnormalised output) records as the fp32 body.
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -181,22 +182,55 @@ __device__ __forceinline__ void split_bf16(float p0, float p1, uint32_t* hi, uin
 
 constexpr int kMmaDkSteps = 8, kMmaDvTiles = 16;   // dk <= 128 (multiple of 16), dv <= 128 (multiple of 8)
 
-__global__ void __launch_bounds__(64) seq_attention_mma_kernel(AttnArgs p) {
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 16 bytes global -> shared without passing through registers; bytes = 0 writes zeros and reads nothing
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     extern __shared__ __align__(16) uint16_t smh[];
-    const int dk = p.dk, dv = p.dv, ldk = dk + 8, ldv = kBK + 8;
-    uint16_t* sK = smh;               // [kBK][ldk]
-    uint16_t* sVt = sK + kBK * ldk;   // [dv][ldv]
+    const int dk = p.dk, dv = p.dv, ldk = dk + 8, ldvr = dv + 8;
+    const int stage_elems = kBK * (ldk + ldvr);   // one stage: K rows [kBK][ldk], then V rows [kBK][ldvr]
     const sllm_seq_batch& b = p.b;
-    const int qt = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    const int qt = blockIdx.x, split = blockIdx.z;
     const int seg = b.qt_seg[qt], off = b.qt_off[qt];
     const int nq = min(kBQ, b.seg_len[seg] - off), t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
-    const int gkv = h / (p.heads / p.kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    // two warps (16 queries each) per head; a CTA of four warps serves two query heads of the same kv head from one staged tile
+    const int hpc = blockDim.x >> 6, h = blockIdx.y * hpc + (warp >> 1), wq = warp & 1;
+    const int gkv = h / (p.heads / p.kv_heads);
     const int dks = dk / 16, dvt = dv / 8;
     const uint16_t* kp = reinterpret_cast<const uint16_t*>(p.k_pool);
     const uint16_t* vp = reinterpret_cast<const uint16_t*>(p.v_pool);
-    const int r0 = warp * 16 + g, r1 = r0 + 8;           // this thread's two query rows inside the tile
+    const int r0 = wq * 16 + g, r1 = r0 + 8;           // this thread's two query rows inside the tile
     const bool ok0 = r0 < nq, ok1 = r1 < nq;
+    const int last_pos = pos0 + nq - 1, nkt = last_pos / kBK + 1;
+
+    // tile kt of the sequence -> stage `st` of shared memory, asynchronously (rows beyond the last position are zero-filled)
+    auto issue = [&](int kt, int st) {
+        const int j0 = kt * kBK;
+        const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
+        const int valid = min(kBK, last_pos + 1 - j0);
+        const uint16_t* ksrc = kp + seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dk);
+        const uint16_t* vsrc = vp + seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dv);
+        uint16_t* sK = smh + st * stage_elems;
+        uint16_t* sV = sK + kBK * ldk;
+        for (int i = threadIdx.x; i < kBK * (dk / 8); i += blockDim.x) {
+            const int r = i / (dk / 8), cc = (i % (dk / 8)) * 8;
+            cp_async16(sK + r * ldk + cc, r < valid ? ksrc + (size_t)r * dk + cc : ksrc, r < valid ? 16 : 0);
+        }
+        for (int i = threadIdx.x; i < kBK * (dv / 8); i += blockDim.x) {
+            const int r = i / (dv / 8), cc = (i % (dv / 8)) * 8;
+            cp_async16(sV + r * ldvr + cc, r < valid ? vsrc + (size_t)r * dv + cc : vsrc, r < valid ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    if (split < nkt) issue(split, 0);
+
     uint32_t qf[kMmaDkSteps][4];
 #pragma unroll
     for (int ks = 0; ks < kMmaDkSteps; ++ks) {
@@ -215,32 +249,21 @@ __global__ void __launch_bounds__(64) seq_attention_mma_kernel(AttnArgs p) {
     float o[kMmaDvTiles][4];
 #pragma unroll
     for (int nt = 0; nt < kMmaDvTiles; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
-    const int last_pos = pos0 + nq - 1, nkt = last_pos / kBK + 1;
-    const int warp_last = pos0 + min(nq - 1, warp * 16 + 15);
-    const bool warp_live = warp * 16 < nq;
-    for (int kt = split; kt < nkt; kt += p.nsplit) {
-        const int j0 = kt * kBK;
-        const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
-        const int valid = min(kBK, last_pos + 1 - j0);
-        const size_t krow = seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dv);
-        __syncthreads();
-        for (int i = threadIdx.x; i < kBK * (dk / 8); i += blockDim.x) {
-            const int r = i / (dk / 8), cc = (i % (dk / 8)) * 8;
-            const uint4 v = r < valid ? *reinterpret_cast<const uint4*>(kp + krow + (size_t)r * dk + cc) : make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(sK + r * ldk + cc) = v;
-        }
-        for (int i = threadIdx.x; i < kBK * (dv / 8); i += blockDim.x) {
-            const int r = i % kBK, cc = (i / kBK) * 8;     // consecutive threads take consecutive keys: the transposed stores spread over the banks
-            const uint4 v = r < valid ? *reinterpret_cast<const uint4*>(vp + vrow + (size_t)r * dv + cc) : make_uint4(0u, 0u, 0u, 0u);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                sVt[(cc + 2 * e) * ldv + r] = (uint16_t)(w[e] & 0xffffu);
-                sVt[(cc + 2 * e + 1) * ldv + r] = (uint16_t)(w[e] >> 16);
-            }
+    const int warp_last = pos0 + min(nq - 1, wq * 16 + 15);
+    const bool warp_live = wq * 16 < nq;
+    int it = 0;
+    for (int kt = split; kt < nkt; kt += p.nsplit, ++it) {
+        const int j0 = kt * kBK, st = it & 1;
+        if (kt + p.nsplit < nkt) {          // the next tile travels while this one is multiplied
+            issue(kt + p.nsplit, st ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
-        if (!warp_live || j0 > warp_last) continue;
+        const uint16_t* sK = smh + st * stage_elems;
+        const uint16_t* sV = sK + kBK * ldk;
+        if (warp_live && j0 <= warp_last) {
         float s[4][4];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
@@ -299,16 +322,19 @@ __global__ void __launch_bounds__(64) seq_attention_mma_kernel(AttnArgs p) {
             split_bf16(s[2 * ks][2], s[2 * ks][3], &ah[1], &al[1]);
             split_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1], &ah[2], &al[2]);
             split_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3], &ah[3], &al[3]);
+            const uint32_t vrow = smem_u32(sV + (ks * 16 + (lane & 15)) * ldvr);   // row-major values: ldmatrix.trans hands out the B fragments
 #pragma unroll
             for (int nt = 0; nt < kMmaDvTiles; ++nt) {
                 if (nt < dvt) {
-                    const uint16_t* vr = sVt + (nt * 8 + g) * ldv + ks * 16 + 2 * c;
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vr), b1 = *reinterpret_cast<const uint32_t*>(vr + 8);
+                    uint32_t b0, b1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(vrow + nt * 16));
                     mma_bf16_16816(o[nt], ah, b0, b1);
                     mma_bf16_16816(o[nt], al, b0, b1);
                 }
             }
         }
+        }
+        __syncthreads();   // everyone is done with this stage before the tile after next lands in it
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -476,8 +502,10 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
     dim3 grid(b->n_qtiles, heads, nsplit);
     // steps that hold a portion of a prompt, bf16 pools, head widths the fragments take: the tensor-core body
     if (kv_dtype == SLLM_BF16 && b->T > b->nseg && dk % 16 == 0 && dk <= 16 * kMmaDkSteps && dv % 8 == 0 && dv <= 8 * kMmaDvTiles && g_tune_seq_attn_mma) {
-        const size_t smem_mma = ((size_t)kBK * (dk + 8) + (size_t)dv * (kBK + 8)) * sizeof(uint16_t);
-        seq_attention_mma_kernel<<<grid, 64, smem_mma, as_stream(stream)>>>(p);
+        const size_t smem_mma = 2 * (size_t)kBK * (dk + 8 + dv + 8) * sizeof(uint16_t);
+        const int hpc = (heads / kv_heads) % 2 == 0 ? 2 : 1;   // query heads per CTA
+        grid.y = heads / hpc;
+        seq_attention_mma_kernel<<<grid, 64 * hpc, smem_mma, as_stream(stream)>>>(p);
         ++g_launches;
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;
