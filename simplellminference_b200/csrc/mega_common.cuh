@@ -8,6 +8,7 @@ namespace sllm {
 constexpr int kMegaThreads = 512;
 constexpr int kMegaWarps = kMegaThreads / 32;
 constexpr int kSlotBytes = 4096;
+static_assert(kSlotBytes == kTileSlotBytes, "tile geometry and ring slot size must agree");
 constexpr int kSlots = 2;
 constexpr int kCplMax = 4;        // max 16-byte chunks per lane per row slice (slice <= 2 KB)
 constexpr int kRoundUnits = 128;  // units per partial-table round

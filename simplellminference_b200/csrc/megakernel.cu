@@ -699,26 +699,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_step_kernel(const MegaPa
 }
 
 // ------------------------------------------------------------------------------------------- host ----
-TileGeom mega_tile_geom(int rows_phys, int cols, int w_dtype) {
-    TileGeom g;
-    const int E = w_dtype == SLLM_F32 ? 4 : w_dtype == SLLM_BF16 ? 8 : 16;
-    g.nchunks = cols / E;
-    int KS = 1;
-    while (KS < 16 && (g.nchunks + KS - 1) / KS * 16 > 1024) KS *= 2;
-    g.KS = KS;
-    g.SC = (g.nchunks + KS - 1) / KS;
-    g.srow = 0;
-    if (w_dtype == SLLM_INT8) {   // a quantisation group = 64 weights = 4 chunks must not straddle K slices; SC/4 scales per row
-        g.SC = (g.SC + 3) / 4 * 4;
-        g.srow = (g.SC + 15) / 16 * 16;
-    }
-    g.R = ((g.SC * 16 + g.srow) * 4 <= kSlotBytes) ? 4 : 2;
-    g.ntr = (rows_phys + g.R - 1) / g.R;
-    g.tile_bytes = g.R * (g.SC * 16 + g.srow);
-    g.bytes = (size_t)g.ntr * g.KS * g.tile_bytes;
-    return g;
-}
-
 static int phys_rows(int rows, int kind) { return kind == PH_GATEUP ? rows : ((rows + 1) / 2) * 2; }
 
 size_t mega_matrix_bytes(int rows, int cols, int kind, int w_dtype) { return mega_tile_geom(phys_rows(rows, kind), cols, w_dtype).bytes; }

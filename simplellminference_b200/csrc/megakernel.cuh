@@ -31,7 +31,27 @@ struct PhaseDesc {       // one weight phase, built on the host
 
 // geometry of a [rows][cols] matrix in the tiled layout
 struct TileGeom { int nchunks, KS, SC, R, ntr, tile_bytes, srow; size_t bytes; };
-TileGeom mega_tile_geom(int rows_phys, int cols, int w_dtype);
+constexpr int kTileSlotBytes = 4096;   // one ring slot of the decode kernels = one tile (mega_common.cuh asserts kSlotBytes equals it)
+// host arithmetic only; inline so that every library that carries the prefill GEMM (which plans its tiles with it) has it
+inline TileGeom mega_tile_geom(int rows_phys, int cols, int w_dtype) {
+    TileGeom g;
+    const int E = w_dtype == SLLM_F32 ? 4 : w_dtype == SLLM_BF16 ? 8 : 16;
+    g.nchunks = cols / E;
+    int KS = 1;
+    while (KS < 16 && (g.nchunks + KS - 1) / KS * 16 > 1024) KS *= 2;
+    g.KS = KS;
+    g.SC = (g.nchunks + KS - 1) / KS;
+    g.srow = 0;
+    if (w_dtype == SLLM_INT8) {   // a quantisation group = 64 weights = 4 chunks must not straddle K slices; SC/4 scales per row
+        g.SC = (g.SC + 3) / 4 * 4;
+        g.srow = (g.SC + 15) / 16 * 16;
+    }
+    g.R = ((g.SC * 16 + g.srow) * 4 <= kTileSlotBytes) ? 4 : 2;
+    g.ntr = (rows_phys + g.R - 1) / g.R;
+    g.tile_bytes = g.R * (g.SC * 16 + g.srow);
+    g.bytes = (size_t)g.ntr * g.KS * g.tile_bytes;
+    return g;
+}
 // bytes of one [rows][cols] matrix of phase kind `kind` in the tiled layout
 size_t mega_matrix_bytes(int rows, int cols, int kind, int w_dtype);
 

@@ -144,3 +144,14 @@ def test_scheduler_with_a_decoder_that_takes_prompts_in_portions():
     for rid, n in zip(ids, lens):
         assert len(out[rid]) == n + new - 1
         assert out[rid][:n - 1].tolist() == list(range(1, n))
+
+
+def test_partial_library_is_self_contained():
+    """The library that carries only the ragged-batch kernels must not need a symbol of the translation units it leaves out."""
+    import subprocess
+    from simplellminference_b200 import _lib
+    if not os.path.exists(_lib.SEQ_LIB_PATH):
+        pytest.skip("partial library not built")
+    out = subprocess.run(["nm", "-D", "--undefined-only", _lib.SEQ_LIB_PATH], capture_output=True, text=True, check=True).stdout
+    missing = [ln.split()[-1] for ln in out.splitlines() if " U " in ln and "sllm" in ln]
+    assert not missing, missing
