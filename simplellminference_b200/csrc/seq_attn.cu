@@ -31,6 +31,7 @@ struct AttnArgs {
     const float* q; int ldq, heads, kv_heads, dk, dv; float scale;
     const void *k_pool, *v_pool;
     int nsplit; float* ws;
+    int by_head;   // fp32 body, steps of single tokens: a CTA's "queries" are the query heads of ONE kv head at one token (they share its tiles)
 };
 
 template <typename KV>
@@ -41,17 +42,23 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     float* sk = sq + kBQ * dkp;          // [kBK][dkp]
     float* sv = sk + kBK * dkp;          // [kBK][dv]
     const sllm_seq_batch& b = p.b;
-    const int qt = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    const int qt = blockIdx.x, split = blockIdx.z;
     const int seg = b.qt_seg[qt], off = b.qt_off[qt];
-    const int nq = min(kBQ, b.seg_len[seg] - off), t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
-    const int g = h / (p.heads / p.kv_heads);
+    const int group = p.heads / p.kv_heads;
+    const int t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
+    // row r of the CTA's query tile is (token t0 + r, head blockIdx.y), or with by_head (token t0, head blockIdx.y * group + r)
+    const int nq = p.by_head ? group : min(kBQ, b.seg_len[seg] - off);
+    const int g = p.by_head ? blockIdx.y : blockIdx.y / group;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const KV* kp = reinterpret_cast<const KV*>(p.k_pool);
     const KV* vp = reinterpret_cast<const KV*>(p.v_pool);
+    auto row_token = [&](int r) { return p.by_head ? t0 : t0 + r; };
+    auto row_head = [&](int r) { return p.by_head ? (int)blockIdx.y * group + r : (int)blockIdx.y; };
+    auto row_pos = [&](int r) { return p.by_head ? pos0 : pos0 + r; };
 
     for (int i = threadIdx.x; i < kBQ * dkp; i += blockDim.x) {
         const int r = i / dkp, c = i % dkp;
-        sq[i] = (r < nq && c < dk) ? p.q[(size_t)(t0 + r) * p.ldq + (size_t)h * dk + c] : 0.0f;
+        sq[i] = (r < nq && c < dk) ? p.q[(size_t)row_token(r) * p.ldq + (size_t)row_head(r) * dk + c] : 0.0f;
     }
     float m[kQW], l[kQW], acc[kQW][kMaxDvChunks];
 #pragma unroll
@@ -61,7 +68,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
 #pragma unroll
         for (int c = 0; c < kMaxDvChunks; ++c) acc[i][c] = 0.0f;
     }
-    const int last_pos = pos0 + nq - 1, nkt = last_pos / kBK + 1;
+    const int last_pos = row_pos(nq - 1), nkt = last_pos / kBK + 1;
     for (int kt = split; kt < nkt; kt += p.nsplit) {
         const int j0 = kt * kBK;
         const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
@@ -116,7 +123,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
 #pragma unroll
         for (int i = 0; i < kQW; ++i) {
             const int qi = warp * kQW + i;
-            const bool see = qi < nq && (j0 + lane) <= (pos0 + qi);
+            const bool see = qi < nq && (j0 + lane) <= row_pos(qi);
             const float sc = see ? s[i] * p.scale : -INFINITY;
             const float mn = fmaxf(m[i], warp_max(sc));
             const float corr = (mn == -INFINITY) ? 1.0f : expf(m[i] - mn);   // m = -inf: nothing accumulated yet, expf(-inf) = 0 is right too
@@ -145,7 +152,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     for (int i = 0; i < kQW; ++i) {
         const int qi = warp * kQW + i;
         if (qi >= nq) continue;
-        float* rec = p.ws + (((size_t)(t0 + qi) * p.heads + h) * p.nsplit + split) * (dv + 2);
+        float* rec = p.ws + (((size_t)row_token(qi) * p.heads + row_head(qi)) * p.nsplit + split) * (dv + 2);
         if (lane == 0) {
             rec[0] = m[i];
             rec[1] = l[i];
@@ -366,36 +373,65 @@ __global__ void seq_attention_finish_kernel(sllm_seq_batch b, const float* __res
     if (item >= b.T * heads) return;
     const int t = item / heads, h = item % heads;
     const float* rec = ws + ((size_t)t * heads + h) * nsplit * (dv + 2);
+    // every share's weight exp(m_s - max) / sum once: lane s holds the weights of shares s, s + 32, ... (up to four: nsplit <= 128 here,
+    // more are folded in a slow loop below)
     float mx = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, rec[(size_t)s * (dv + 2)]);
-    float den = 0.0f;
-    for (int s = 0; s < nsplit; ++s) {
+    for (int s = lane; s < nsplit; s += 32) mx = fmaxf(mx, rec[(size_t)s * (dv + 2)]);
+    mx = warp_max(mx);
+    float wgt[4] = {0.0f, 0.0f, 0.0f, 0.0f}, den = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int s = lane + 32 * j;
+        if (s < nsplit) {
+            const float ms = rec[(size_t)s * (dv + 2)];
+            wgt[j] = ms == -INFINITY ? 0.0f : expf(ms - mx);
+            den += rec[(size_t)s * (dv + 2) + 1] * wgt[j];
+        }
+    }
+    for (int s = 128 + lane; s < nsplit; s += 32) {
         const float ms = rec[(size_t)s * (dv + 2)];
         if (ms != -INFINITY) den += rec[(size_t)s * (dv + 2) + 1] * expf(ms - mx);
     }
+    den = warp_sum(den);
+    const float inv_den = 1.0f / den;
     const float gv = gate ? seq_sigmoid(gate[(size_t)t * ldg + h]) : 1.0f;
     const int pos = b.tok_pos[t];
     float* orow = out + (size_t)t * ldo + (size_t)h * dv;
-    auto merged = [&](int col) {
+    auto merged = [&](int col) {      // called by all lanes together (the weights travel by shuffle); col may lie beyond dv
         float v = 0.0f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float ms = rec[(size_t)s * (dv + 2)];
-            if (ms != -INFINITY) v += rec[(size_t)s * (dv + 2) + 2 + col] * expf(ms - mx);
+        const bool in = col < dv;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            for (int s0 = 0; s0 < 32 && 32 * j + s0 < nsplit; ++s0) {
+                const float w = __shfl_sync(0xffffffffu, wgt[j], s0);
+                if (in) v = fmaf(w, rec[(size_t)(32 * j + s0) * (dv + 2) + 2 + col], v);
+            }
         }
-        return v / den;
+        for (int s = 128; s < nsplit; ++s) {
+            const float ms = rec[(size_t)s * (dv + 2)];
+            if (in && ms != -INFINITY) v = fmaf(expf(ms - mx), rec[(size_t)s * (dv + 2) + 2 + col], v);
+        }
+        return v * inv_den;
     };
     if (!vfreq) {
-        for (int col = lane; col < dv; col += 32) orow[col] = merged(col) * gv;
+        for (int c0 = 0; c0 < dv; c0 += 32) {
+            const float v = merged(c0 + lane);
+            if (c0 + lane < dv) orow[c0 + lane] = v * gv;
+        }
         return;
     }
     const int half = dv / 2;
-    for (int mi = lane; mi < half; mi += 32) {
+    for (int m0 = 0; m0 < half; m0 += 32) {
+        const int mi = m0 + lane;
+        const bool in = mi < half;
         const int ia = layout == 0 ? 2 * mi : mi, ib = layout == 0 ? 2 * mi + 1 : mi + half;
-        const float u = merged(ia), v = merged(ib);
-        float sn, cs;
-        seq_angle(pos, vfreq[mi], &sn, &cs);
-        orow[ia] = (u * cs + v * sn) * gv;    // rotation by the negative angle
-        orow[ib] = (v * cs - u * sn) * gv;
+        const float u = merged(in ? ia : dv), v = merged(in ? ib : dv);
+        if (in) {
+            float sn, cs;
+            seq_angle(pos, vfreq[mi], &sn, &cs);
+            orow[ia] = (u * cs + v * sn) * gv;    // rotation by the negative angle
+            orow[ib] = (v * cs - u * sn) * gv;
+        }
     }
 }
 
@@ -498,7 +534,7 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
     const int dkp = ((dk + 3) & ~3) + 4;
     const size_t smem = ((size_t)(kBQ + kBK) * dkp + (size_t)kBK * dv) * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes(), SLLM_ENOTSUP, "seq_attention: heads of %d + %d floats need %zu bytes of shared memory", dk, dv, smem);
-    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws};
+    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0};
     dim3 grid(b->n_qtiles, heads, nsplit);
     // steps that hold a portion of a prompt, bf16 pools, head widths the fragments take: the tensor-core body
     if (kv_dtype == SLLM_BF16 && b->T > b->nseg && dk % 16 == 0 && dk <= 16 * kMmaDkSteps && dv % 8 == 0 && dv <= 8 * kMmaDvTiles && g_tune_seq_attn_mma) {
@@ -509,6 +545,10 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
         ++g_launches;
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;
+    }
+    if (b->T == b->nseg && heads / kv_heads <= kBQ) {   // single tokens only: the query heads of a kv head share one CTA and its tiles
+        p.by_head = 1;
+        grid.y = kv_heads;
     }
     if (kv_dtype == SLLM_F32) {
         if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

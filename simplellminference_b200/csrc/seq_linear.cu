@@ -1,6 +1,7 @@
 // csrc/seq_linear.cu — sllm_seq_linear: C = alpha * (A . W^T + bias) (+ C) for the ragged token batch. Three bodies:
-//   * rows_kernel  (T <= 8, decode-sized steps): one warp per output column streams that weight row once with 16-byte loads and keeps one
-//     accumulator per activation row — bandwidth-bound like the GEMV of the one-sequence path, any shape (scalar loads when unaligned);
+//   * rows_kernel  (T <= 8, decode-sized steps): 1 to 8 warps per output column stream that weight row once with 16-byte loads, four in
+//     flight per lane, one accumulator per activation row — the bandwidth-bound shape of the one-sequence path's GEMV, any size (scalar
+//     loads when unaligned);
 //   * tile_kernel  (any shape): 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMAs with fp32 accumulation. This is
 //     the body of the all-fp32 mode, and of bf16 products whose shape the tensor-core tiles do not take;
 //   * the tcgen05 GEMM of the prefill path (prefill_gemm.cu) for bf16 weights when the caller passes a bf16 scratch for A and the shape
@@ -22,38 +23,64 @@ struct LinArgs {
 
 constexpr int kRowsMax = 8;
 
+// `wpr` warps (1, 2, 4 or 8) share one output column and cut K among them, so that a matrix with few rows and long rows still fills the
+// machine; a lane keeps four 16-byte weight loads in flight. The partial sums of a column meet in shared memory in a fixed order.
 template <int WD>
-__global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec) {
+__global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec, int wpr) {
+    __shared__ float part_sum[8][kRowsMax];
     const int b = blockIdx.y;
     const float* A = p.A + (size_t)b * p.a_bs;
     const float* bias = p.bias ? p.bias + (size_t)b * p.bias_bs : nullptr;
     float* C = p.C + (size_t)b * p.c_bs;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp;
-    if (n >= p.N) return;
+    const int item = blockIdx.x * 8 + warp, n = item / wpr, part = item % wpr;
+    constexpr int E = WD == SLLM_BF16 ? 8 : 4;                 // weights per 16-byte load
+    const int kper = ((p.K + wpr - 1) / wpr + E - 1) / E * E;  // this warp's share of K, a multiple of the load width
+    const int k_lo = part * kper, k_hi = min(p.K, k_lo + kper);
     float acc[kRowsMax];
 #pragma unroll
     for (int t = 0; t < kRowsMax; ++t) acc[t] = 0.0f;
-    if (WD == SLLM_BF16) {
-        const uint16_t* w = reinterpret_cast<const uint16_t*>(p.W) + (size_t)b * p.w_bs + (size_t)n * p.ldw;
+    if (n < p.N) {
         if (vec) {
-            for (int k = lane * 8; k < p.K; k += 256) {
-                const uint4 u = ldg_stream(w + k);
-                const float wv[8] = {bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y), bf16_lo(u.z), bf16_hi(u.z), bf16_lo(u.w), bf16_hi(u.w)};
+            const uint8_t* w = reinterpret_cast<const uint8_t*>(p.W) + ((size_t)b * p.w_bs + (size_t)n * p.ldw) * (16 / E);
+            for (int k0 = k_lo + lane * E; k0 < k_hi; k0 += 4 * 32 * E) {
+                uint4 u[4];
 #pragma unroll
-                for (int t = 0; t < kRowsMax; ++t) {
-                    if (t < p.T) {
-                        const float4 a0 = *reinterpret_cast<const float4*>(A + (size_t)t * p.lda + k);
-                        const float4 a1 = *reinterpret_cast<const float4*>(A + (size_t)t * p.lda + k + 4);
-                        float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                for (int j = 0; j < 4; ++j) {
+                    const int k = k0 + j * 32 * E;
+                    u[j] = k < k_hi ? ldg_stream(w + (size_t)k * (16 / E)) : make_uint4(0u, 0u, 0u, 0u);
+                }
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[t] = fmaf(p.round_a ? seq_round_bf16(av[e]) : av[e], wv[e], acc[t]);
+                for (int j = 0; j < 4; ++j) {
+                    const int k = k0 + j * 32 * E;
+                    if (k < k_hi) {
+                        float wv[E];
+                        if (WD == SLLM_BF16) {
+                            wv[0] = bf16_lo(u[j].x); wv[1] = bf16_hi(u[j].x); wv[2] = bf16_lo(u[j].y); wv[3] = bf16_hi(u[j].y);
+                            wv[E - 4] = bf16_lo(u[j].z); wv[E - 3] = bf16_hi(u[j].z); wv[E - 2] = bf16_lo(u[j].w); wv[E - 1] = bf16_hi(u[j].w);
+                        } else {
+                            wv[0] = __uint_as_float(u[j].x); wv[1] = __uint_as_float(u[j].y); wv[2] = __uint_as_float(u[j].z); wv[3] = __uint_as_float(u[j].w);
+                        }
+#pragma unroll
+                        for (int t = 0; t < kRowsMax; ++t) {
+                            if (t < p.T) {
+                                const float* ar = A + (size_t)t * p.lda + k;
+#pragma unroll
+                                for (int e = 0; e < E; e += 4) {
+                                    const float4 a4 = *reinterpret_cast<const float4*>(ar + e);
+                                    const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) acc[t] = fmaf(p.round_a ? seq_round_bf16(av[i]) : av[i], wv[e + i], acc[t]);
+                                }
+                            }
+                        }
                     }
                 }
             }
         } else {
-            for (int k = lane; k < p.K; k += 32) {
-                const float wv = seq_ld(w, k);
+            for (int k = k_lo + lane; k < k_hi; k += 32) {
+                const size_t wi = (size_t)b * p.w_bs + (size_t)n * p.ldw + k;
+                const float wv = WD == SLLM_BF16 ? seq_ld(reinterpret_cast<const uint16_t*>(p.W), wi) : reinterpret_cast<const float*>(p.W)[wi];
 #pragma unroll
                 for (int t = 0; t < kRowsMax; ++t)
                     if (t < p.T) {
@@ -62,42 +89,19 @@ __global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec
                     }
             }
         }
-    } else {
-        const float* w = reinterpret_cast<const float*>(p.W) + (size_t)b * p.w_bs + (size_t)n * p.ldw;
-        if (vec) {
-            for (int k = lane * 4; k < p.K; k += 128) {
-                const uint4 u = ldg_stream(w + k);
-                const float wv[4] = {__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w)};
-#pragma unroll
-                for (int t = 0; t < kRowsMax; ++t) {
-                    if (t < p.T) {
-                        const float4 a0 = *reinterpret_cast<const float4*>(A + (size_t)t * p.lda + k);
-                        acc[t] = fmaf(a0.x, wv[0], acc[t]);
-                        acc[t] = fmaf(a0.y, wv[1], acc[t]);
-                        acc[t] = fmaf(a0.z, wv[2], acc[t]);
-                        acc[t] = fmaf(a0.w, wv[3], acc[t]);
-                    }
-                }
-            }
-        } else {
-            for (int k = lane; k < p.K; k += 32) {
-                const float wv = w[k];
-#pragma unroll
-                for (int t = 0; t < kRowsMax; ++t)
-                    if (t < p.T) acc[t] = fmaf(A[(size_t)t * p.lda + k], wv, acc[t]);
-            }
-        }
     }
 #pragma unroll
     for (int t = 0; t < kRowsMax; ++t) {
-        if (t < p.T) {
-            const float s = warp_sum(acc[t]);
-            if (lane == 0) {
-                float v = p.alpha * (s + (bias ? bias[n] : 0.0f));
-                float* c = C + (size_t)t * p.ldc + n;
-                *c = p.accumulate ? *c + v : v;
-            }
-        }
+        const float sum = warp_sum(acc[t]);
+        if (lane == 0) part_sum[warp][t] = sum;
+    }
+    __syncthreads();
+    if (part == 0 && n < p.N && lane < p.T) {
+        float sum = 0.0f;
+        for (int j = 0; j < wpr; ++j) sum += part_sum[warp + j][lane];
+        const float v = p.alpha * (sum + (bias ? bias[n] : 0.0f));
+        float* c = C + (size_t)lane * p.ldc + n;
+        *c = p.accumulate ? *c + v : v;
     }
 }
 
@@ -202,9 +206,11 @@ extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32
         const int e = w_dtype == SLLM_BF16 ? 8 : 4;   // elements per 16-byte weight load
         const bool vec = K % e == 0 && ldw % e == 0 && (w_bs % e) == 0 && lda % 4 == 0 && (a_bs % 4) == 0 &&
                          ((uintptr_t)W % 16) == 0 && ((uintptr_t)A % 16) == 0;
-        dim3 grid((N + 7) / 8, batch);
-        if (w_dtype == SLLM_BF16) seq_linear_rows_kernel<SLLM_BF16><<<grid, 256, 0, st>>>(p, vec);
-        else seq_linear_rows_kernel<SLLM_F32><<<grid, 256, 0, st>>>(p, vec);
+        int wpr = 1;   // warps per output column: enough CTAs for ~4 per SM, and no warp with less than 256 weights
+        while (wpr < 8 && (long long)N * batch * wpr / 8 < 4LL * sm_count() && K / (2 * wpr) >= 256) wpr *= 2;
+        dim3 grid(((long long)N * wpr + 7) / 8, batch);
+        if (w_dtype == SLLM_BF16) seq_linear_rows_kernel<SLLM_BF16><<<grid, 256, 0, st>>>(p, vec, wpr);
+        else seq_linear_rows_kernel<SLLM_F32><<<grid, 256, 0, st>>>(p, vec, wpr);
         ++g_launches;
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;

@@ -176,7 +176,7 @@ def test_norm_streams_polynorm_kernels():
         assert _rel(zt.cpu().numpy(), want) < 1e-6
 
 
-@pytest.mark.parametrize("T,N,K,batch", [(1, 6, 48, 1), (3, 50, 16, 1), (8, 33, 100, 2), (9, 6, 48, 1), (70, 130, 52, 1), (64, 64, 64, 3), (200, 97, 36, 1)])
+@pytest.mark.parametrize("T,N,K,batch", [(1, 6, 48, 1), (3, 50, 16, 1), (8, 33, 100, 2), (2, 16, 4096, 1), (5, 40, 2056, 1), (4, 24, 1030, 2), (9, 6, 48, 1), (70, 130, 52, 1), (64, 64, 64, 3), (200, 97, 36, 1)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_linear_every_body(T, N, K, batch, dtype):
     """The projection kernel at decode-sized and tile-sized row counts, odd shapes, block-diagonal batches, bias, scale and accumulation."""
