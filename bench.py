@@ -648,7 +648,7 @@ def main():
         hbm, hbm_src = peaks()
         tf, tf_src = tensor_peak()
         real = sys.stdout
-        sys.stdout = sys.stderr                      # the per-size lines are progress; the contract is ONE line on stdout
+        sys.stdout = sys.stderr                      # the per-size lines are progress; stdout carries exactly ONE line
         res = bench_hybrid.main(sizes, hbm, tf)
         sys.stdout = real
         print(json.dumps({"hybrid": res, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf, "bf16_source": tf_src}}))

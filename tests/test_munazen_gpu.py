@@ -199,6 +199,35 @@ def test_linear_every_body(T, N, K, batch, dtype):
     assert _rel(Ct.cpu().numpy().reshape(T, batch, N), want) < 2e-6
 
 
+@pytest.mark.parametrize("T,N,K", [(64, 64, 64), (70, 132, 72), (130, 100, 200), (257, 36 * 4, 8 * 13), (1000, 516, 192), (65, 2048, 1024)])
+@pytest.mark.parametrize("bias,alpha,accumulate", [(False, 1.0, False), (False, 1.0, True), (True, 0.7, True), (True, 1.0, False)])
+def test_linear_on_the_tensor_cores(T, N, K, bias, alpha, accumulate):
+    """Steps of 64 tokens and more hand bf16 products to the tcgen05 GEMM: tile edges in every dimension, the direct store / add
+    epilogues and the bias / scale epilogue kernel, against the same operands in float64."""
+    import torch
+
+    from simplellminference_b200.config import BF16
+    from simplellminference_b200.seqops import Ops
+    ops, dev, rng = Ops(BF16), torch.device("cuda"), np.random.default_rng(T + N + K)
+    st = torch.cuda.current_stream().cuda_stream
+    lda, ldc = K + 8, N + 4
+    A = rng.standard_normal((T, lda)).astype(np.float32)
+    W = L.bf16_round(rng.standard_normal((N, K)))
+    b = rng.standard_normal(N).astype(np.float32) if bias else None
+    C0 = rng.standard_normal((T, ldc)).astype(np.float32)
+    At, Ct = torch.tensor(A, device=dev), torch.tensor(C0, device=dev)
+    Wt = torch.tensor(W, device=dev, dtype=torch.bfloat16)
+    scratch = torch.empty((((T * K * 2 + 255) // 256) * 256 + T * N * 4 + 3) // 4, dtype=torch.float32, device=dev)
+    ops.linear(At.data_ptr(), lda, Wt, K, torch.tensor(b, device=dev) if bias else None, Ct.data_ptr(), ldc, T, N, K, st, alpha=alpha,
+               accumulate=accumulate, scratch=scratch)
+    want = alpha * (L.bf16_round(A[:, :K]).astype(np.float64) @ W.astype(np.float64).T + (b if bias else 0.0))
+    if accumulate:
+        want = want + C0[:, :N]
+    got = Ct.cpu().numpy()
+    assert _rel(got[:, :N], want) < 2e-6
+    np.testing.assert_array_equal(got[:, N:], C0[:, N:])      # the padding columns of the output rows stay untouched
+
+
 # ------------------------------------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("cfg", [CFG_A, CFG_ONES], ids=["mixed", "ones"])
 def test_whole_prompt_matches_oracle_fp32_and_layers(tmp_path, cfg):
@@ -213,7 +242,15 @@ def test_whole_prompt_matches_oracle_fp32_and_layers(tmp_path, cfg):
     assert L.logit_error(out, want).max() < F32_TOL
 
 
-def test_bf16_mode_within_operand_rounding(tmp_path):
+# head geometries for the tensor-core attention body: three query heads on one kv head (one head per CTA), one on one, widths 32 / 16 / 40
+CFG_B = L.make_config([L.parallel_layer(heads=3, kv_heads=1, dim=32, vdim=16, rot_dims=16, width=32, blocks=4, ff=None),
+                       L.parallel_layer(heads=2, kv_heads=2, dim=16, vdim=40, rot_dims=16, scaling=SCALING, width=16, blocks=1, conv=2, ff=64),
+                       L.gla_layer(heads=2, dim=16, vdim=32, ff=None)], vocab=128, width=64, streams=2, groups=4)
+
+
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_B], ids=["mixed", "heads"])
+def test_bf16_mode_within_operand_rounding(tmp_path, cfg):
+    CFG_A = cfg   # noqa: N806  (the body below was written for one configuration)
     w = L.random_weights(CFG_A, seed=4)
     toks = np.random.default_rng(1).integers(0, CFG_A["vocab"], size=120).tolist()
     want = O.forward(CFG_A, w, toks)
