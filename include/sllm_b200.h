@@ -423,6 +423,10 @@ int sllm_seq_hyper_read(const float* x, int32_t streams, int32_t T, int32_t d, c
 /* all streams at once from the old ones: x[t] <- sum_s mix[s][t] * x[s] + outc[t] * y (mix NULL = identity, outc NULL = ones) */
 int sllm_seq_hyper_write(float* x, int32_t streams, int32_t T, int32_t d, const float* mix, const float* outc, const float* y,
                          sllm_stream_t stream);
+/* sllm_seq_hyper_write (mix, outc, y_in) followed by sllm_seq_hyper_read (coef, norm_w, groups, eps -> y_out) of the next sublayer, as one
+ * pass over the streams; y_in and y_out must differ. */
+int sllm_seq_hyper_write_read(float* x, int32_t streams, int32_t T, int32_t d, const float* mix, const float* outc, const float* y_in,
+                              const float* coef, const float* norm_w, int32_t groups, float eps, float* y_out, sllm_stream_t stream);
 /* C[b] = alpha * (A[b] . W[b]^T + bias[b]) (+ C[b] if accumulate): A fp32 [T][lda] (rounded to bf16 on load if round_a), W [N][ldw]
  * row-major in w_dtype, bias fp32 [N] or NULL, C fp32 [T][ldc]; `batch` independent products whose operands lie *_bs elements apart
  * (block-diagonal matrices). Any T, N, K. With a16 (scratch of T*K bf16 values) given, bf16 weights and a shape its tiles take, the

@@ -59,6 +59,45 @@ __global__ void seq_hyper_write_kernel(float* __restrict__ x, int streams, int T
     }
 }
 
+// hyper-connection write of one sublayer and read (+ grouped norm) of the next in one pass over the streams: grid (T, groups), a CTA owns
+// one part of one token's vector in every stream — it stores the mixed streams and normalises their weighted sum for the next sublayer
+__global__ void seq_hyper_write_read_kernel(float* __restrict__ x, int streams, int T, int d, const float* __restrict__ mix, const float* __restrict__ outc,
+                                            const float* __restrict__ y_in, const float* __restrict__ coef, const float* __restrict__ norm_w, int groups,
+                                            float eps, float* __restrict__ y_out) {
+    __shared__ float red[33];
+    const int t = blockIdx.x, g = blockIdx.y, n = d / groups, j0 = g * n;
+    const size_t plane = (size_t)T * d;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const size_t i = (size_t)t * d + j0 + j;
+        float old[kMaxStreams];
+        for (int s = 0; s < streams; ++s) old[s] = x[(size_t)s * plane + i];
+        const float yv = y_in[i];
+        float u = 0.0f;
+        for (int to = 0; to < streams; ++to) {
+            float v;
+            if (mix) {
+                v = 0.0f;
+                for (int s = 0; s < streams; ++s) v = fmaf(mix[s * streams + to], old[s], v);
+            } else {
+                v = old[to];
+            }
+            v = fmaf(outc ? outc[to] : 1.0f, yv, v);
+            x[(size_t)to * plane + i] = v;
+            u = fmaf(coef ? coef[to] : 1.0f, v, u);
+        }
+        y_out[i] = u;
+        ss = fmaf(u, u, ss);
+    }
+    if (!norm_w) return;
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const size_t i = (size_t)t * d + j0 + j;
+        y_out[i] = (y_out[i] * inv) * norm_w[j0 + j];
+    }
+}
+
 __global__ void seq_polynorm_kernel(const float* z, int ldz, const float* __restrict__ coef, float eps, float* out,
                                     int ldo, int n) {
     __shared__ float red[33];
@@ -139,6 +178,19 @@ int sllm_seq_hyper_write(float* x, int32_t streams, int32_t T, int32_t d, const 
     const size_t n = (size_t)T * d;
     const int blocks = (int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8);
     seq_hyper_write_kernel<<<blocks, 256, 0, as_stream(stream)>>>(x, streams, T, d, mix, outc, y);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_hyper_write_read(float* x, int32_t streams, int32_t T, int32_t d, const float* mix, const float* outc, const float* y_in, const float* coef,
+                              const float* norm_w, int32_t groups, float eps, float* y_out, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && y_in && y_out && y_in != y_out && T > 0 && d > 0, SLLM_EINVAL, "seq_hyper_write_read: bad argument");
+    SLLM_REQUIRE(streams >= 1 && streams <= kMaxStreams, SLLM_ENOTSUP, "seq_hyper_write_read: 1..%d streams", kMaxStreams);
+    if (!norm_w) groups = 1;
+    SLLM_REQUIRE(groups >= 1 && d % groups == 0, SLLM_EINVAL, "seq_hyper_write_read: %d does not divide into %d parts", d, groups);
+    const int n = d / groups, threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+    seq_hyper_write_read_kernel<<<dim3(T, groups), threads, 0, as_stream(stream)>>>(x, streams, T, d, mix, outc, y_in, coef, norm_w, groups, eps, y_out);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -55,17 +55,30 @@ class MunazenModel:
         h = step.scratch("normed", T * d)
         y = step.scratch("sub_out", T * d)
         ops.embed(ids, self.embed, self.vocab, d, S, x, T, step.st)
-        for r, li in enumerate(self.runs):
-            for sub in self.layers[li]:
-                ops.hyper_read(x, S, T, d, sub.hc_in, sub.norm_w, c.norm_groups, c.norm_eps, h, step.st)
-                sub.body.forward(step, h, states[r], y)
+        # the sublayers in the order they run; between two of them the write of the first and the read (+ norm) of the second are one kernel
+        chain = [(r, k, sub) for r, li in enumerate(self.runs) for k, sub in enumerate(self.layers[li])]
+        first = chain[0][2]
+        ops.hyper_read(x, S, T, d, first.hc_in, first.norm_w, c.norm_groups, c.norm_eps, h, step.st)
+        for i, (r, k, sub) in enumerate(chain):
+            sub.body.forward(step, h, states[r], y)
+            last_of_run = i + 1 == len(chain) or chain[i + 1][0] != r
+            nxt = chain[i + 1][2] if i + 1 < len(chain) else None
+            if tap is not None and last_of_run:          # inspection of the stream sum after a layer run: the unfused kernels
                 ops.hyper_write(x, S, T, d, sub.hc_mix, sub.hc_out, y, step.st)
-            if tap is not None:
                 ops.hyper_read(x, S, T, d, None, None, 1, 0.0, h, step.st)
                 tap(r, h[:T * d].view(T, d))
+                if nxt is not None:
+                    ops.hyper_read(x, S, T, d, nxt.hc_in, nxt.norm_w, c.norm_groups, c.norm_eps, h, step.st)
+                elif n_rows:
+                    ops.hyper_read(x, S, T, d, None, self.final_norm, c.norm_groups, c.norm_eps, h, step.st)
+            elif nxt is not None:
+                ops.hyper_write_read(x, S, T, d, sub.hc_mix, sub.hc_out, y, nxt.hc_in, nxt.norm_w, c.norm_groups, c.norm_eps, h, step.st)
+            elif n_rows:                                 # after the last sublayer: the sum of the streams through the model's norm
+                ops.hyper_write_read(x, S, T, d, sub.hc_mix, sub.hc_out, y, None, self.final_norm, c.norm_groups, c.norm_eps, h, step.st)
+            else:
+                ops.hyper_write(x, S, T, d, sub.hc_mix, sub.hc_out, y, step.st)
         if n_rows == 0:
             return None
-        ops.hyper_read(x, S, T, d, None, self.final_norm, c.norm_groups, c.norm_eps, h, step.st)
         picked = step.scratch("picked", n_rows * d)
         ops.gather_rows(h, d, rows, n_rows, d, picked, step.st)
         logits = step.scratch("logits", n_rows * self.vocab)

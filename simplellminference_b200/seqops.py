@@ -45,6 +45,9 @@ class Ops:
     def hyper_write(self, x, streams, T, d, mix, outc, y, st):
         self._ck(self.lib.sllm_seq_hyper_write(_p(x), streams, T, d, _p(mix), _p(outc), _p(y), st))
 
+    def hyper_write_read(self, x, streams, T, d, mix, outc, y_in, coef, norm_w, groups, eps, y_out, st):
+        self._ck(self.lib.sllm_seq_hyper_write_read(_p(x), streams, T, d, _p(mix), _p(outc), _p(y_in), _p(coef), _p(norm_w), groups, eps, _p(y_out), st))
+
     def linear(self, a_ptr, lda, w, ldw, bias, c_ptr, ldc, T, N, K, st, alpha=1.0, accumulate=False, batch=1, a_bs=0, w_bs=0, bias_bs=0,
                c_bs=0, scratch=None):
         self._ck(self.lib.sllm_seq_linear(a_ptr, lda, _p(w), self.w_dtype, ldw, _p(bias), c_ptr, ldc, T, N, K, alpha, int(accumulate),

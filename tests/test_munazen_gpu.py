@@ -166,6 +166,14 @@ def test_norm_streams_polynorm_kernels():
         ops.hyper_write(xt, S, T, d, torch.tensor(mix, device=dev), torch.tensor(outc, device=dev), torch.tensor(y, device=dev), st)
         want = np.einsum("st,sij->tij", mix.astype(np.float64), x.astype(np.float64)) + outc[:, None, None] * y[None].astype(np.float64)
         assert _rel(xt.cpu().numpy(), want) < 1e-6
+        # the fused form (write of one sublayer + read and norm of the next) against the two kernels, bit for bit
+        x2, x3 = torch.tensor(x, device=dev), torch.tensor(x, device=dev)
+        o2, o3 = torch.empty(T * d, device=dev), torch.empty(T * d, device=dev)
+        args = (torch.tensor(mix, device=dev), torch.tensor(outc, device=dev), torch.tensor(y, device=dev))
+        ops.hyper_write(x2, S, T, d, *args, st)
+        ops.hyper_read(x2, S, T, d, torch.tensor(coef, device=dev), torch.tensor(wn, device=dev), groups, 1e-5, o2, st)
+        ops.hyper_write_read(x3, S, T, d, *args, torch.tensor(coef, device=dev), torch.tensor(wn, device=dev), groups, 1e-5, o3, st)
+        assert torch.equal(x2, x3) and torch.equal(o2, o3)
     for T, n in ((4, 24), (3, 700)):
         z = rng.standard_normal((T, n)).astype(np.float32)
         coef = np.array([0.6, 0.3, -0.2, 0.05], np.float32)
