@@ -430,3 +430,31 @@ def test_trace_replayer_command(tmp_path):
     assert L.logit_error(got0, wa[[0, 29]]).max() < F32_TOL
     assert L.logit_error(got1, np.stack([wa[30], wb[8]])).max() < F32_TOL
     assert L.logit_error(got3, wb[[0, 8]]).max() < F32_TOL
+
+
+def test_generation_command_line(tmp_path):
+    """python -m simplellminference_b200.generate: two prompts of token ids through the registry, the engine and the scheduler; the greedy
+    continuation equals the restatement's (near ties may fall either way and are then followed)."""
+    import json
+    import subprocess
+    cfg = CFG_ONES
+    w = L.random_weights(cfg, seed=21)
+    folder = L.write_model(str(tmp_path / "model"), cfg, w)
+    prompts = [[3, 1, 4, 1, 5, 9, 2, 6], [7]]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "simplellminference_b200.generate", "--model", folder, "--dtype", "float32", "--max-new-tokens", "6", "--prefill-chunk", "3"]
+    for p in prompts:
+        cmd += ["--prompt", ",".join(str(t) for t in p)]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert [ln["prompt"] for ln in lines] == prompts
+    for ln in lines:
+        seq = list(ln["prompt"])
+        assert len(ln["tokens"]) == 6
+        for tok in ln["tokens"]:
+            lg = O.forward(cfg, w, seq)[-1]
+            order = np.argsort(lg)
+            close = lg[order[-1]] - lg[order[-2]] <= 1e-3 * np.abs(lg).max()
+            assert tok == int(order[-1]) or (close and tok == int(order[-2])), (seq, tok)
+            seq.append(tok)
