@@ -2,6 +2,8 @@
 #pragma once
 #include <algorithm>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace sllm {
@@ -27,7 +29,8 @@ __device__ __forceinline__ void seq_ld16(const uint16_t* p, bool take, float (&o
 }
 __device__ __forceinline__ void seq_st(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void seq_st(uint16_t* p, size_t i, float v) { p[i] = f32_to_bf16_bits(v); }
-__device__ __forceinline__ float seq_round_bf16(float v) { return __uint_as_float((uint32_t)f32_to_bf16_bits(v) << 16); }
+// nearest-even rounding to bf16 and back: one cvt instruction + one shift (the same values as f32_to_bf16_bits for finite inputs)
+__device__ __forceinline__ float seq_round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 __device__ __forceinline__ float seq_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 // log(1 + e^z) without overflow
