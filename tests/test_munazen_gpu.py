@@ -256,7 +256,12 @@ CFG_B = L.make_config([L.parallel_layer(heads=3, kv_heads=1, dim=32, vdim=16, ro
                        L.gla_layer(heads=2, dim=16, vdim=32, ff=None)], vocab=128, width=64, streams=2, groups=4)
 
 
-@pytest.mark.parametrize("cfg", [CFG_A, CFG_B], ids=["mixed", "heads"])
+# every fused projection is wide enough and a multiple of 4 columns: steps of 64 tokens and more run them on the tcgen05 GEMM
+CFG_C = L.make_config([L.gla_layer(heads=2, dim=16, vdim=32, ff=128), L.parallel_layer(heads=4, kv_heads=2, dim=16, vdim=16, rot_dims=8, width=32, blocks=2, ff=128)],
+                      vocab=256, width=64, streams=2, groups=2, loop={"start": 0, "stop": 2, "times": 2})
+
+
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_B, CFG_C], ids=["mixed", "heads", "tensorcore"])
 def test_bf16_mode_within_operand_rounding(tmp_path, cfg):
     CFG_A = cfg   # noqa: N806  (the body below was written for one configuration)
     w = L.random_weights(CFG_A, seed=4)
