@@ -366,72 +366,54 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     }
 }
 
-// one warp per (token, head): merge the shares, normalise, turn back by the token's position, gate
+// one CTA per (token, head), one thread per value column: merge the shares, normalise, turn back by the token's position, gate.
+// Warp 0 turns the shares' (max, sum) into one weight per share (exp(m_s - max) / total, zero for a share that saw no key); every thread
+// then adds its column over the shares with coalesced loads; pairs meet through shared memory for the rotation.
 __global__ void seq_attention_finish_kernel(sllm_seq_batch b, const float* __restrict__ ws, int nsplit, int heads, int dv, const double* __restrict__ vfreq,
                                             int layout, const float* __restrict__ gate, int ldg, float* __restrict__ out, int ldo) {
-    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (item >= b.T * heads) return;
-    const int t = item / heads, h = item % heads;
+    extern __shared__ float fsm[];
+    float* s_w = fsm;            // [nsplit]
+    float* s_o = fsm + nsplit;   // [dv]
+    const int t = blockIdx.x / heads, h = blockIdx.x % heads, lane = threadIdx.x & 31;
     const float* rec = ws + ((size_t)t * heads + h) * nsplit * (dv + 2);
-    // every share's weight exp(m_s - max) / sum once: lane s holds the weights of shares s, s + 32, ... (up to four: nsplit <= 128 here,
-    // more are folded in a slow loop below)
-    float mx = -INFINITY;
-    for (int s = lane; s < nsplit; s += 32) mx = fmaxf(mx, rec[(size_t)s * (dv + 2)]);
-    mx = warp_max(mx);
-    float wgt[4] = {0.0f, 0.0f, 0.0f, 0.0f}, den = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int s = lane + 32 * j;
-        if (s < nsplit) {
+    if (threadIdx.x < 32) {
+        float mx = -INFINITY;
+        for (int s = lane; s < nsplit; s += 32) mx = fmaxf(mx, rec[(size_t)s * (dv + 2)]);
+        mx = warp_max(mx);
+        float den = 0.0f;
+        for (int s = lane; s < nsplit; s += 32) {
             const float ms = rec[(size_t)s * (dv + 2)];
-            wgt[j] = ms == -INFINITY ? 0.0f : expf(ms - mx);
-            den += rec[(size_t)s * (dv + 2) + 1] * wgt[j];
+            const float w = ms == -INFINITY ? 0.0f : expf(ms - mx);
+            s_w[s] = w;
+            den = fmaf(rec[(size_t)s * (dv + 2) + 1], w, den);
         }
+        den = warp_sum(den);
+        const float inv_den = 1.0f / den;
+        for (int s = lane; s < nsplit; s += 32) s_w[s] *= inv_den;
     }
-    for (int s = 128 + lane; s < nsplit; s += 32) {
-        const float ms = rec[(size_t)s * (dv + 2)];
-        if (ms != -INFINITY) den += rec[(size_t)s * (dv + 2) + 1] * expf(ms - mx);
-    }
-    den = warp_sum(den);
-    const float inv_den = 1.0f / den;
-    const float gv = gate ? seq_sigmoid(gate[(size_t)t * ldg + h]) : 1.0f;
-    const int pos = b.tok_pos[t];
-    float* orow = out + (size_t)t * ldo + (size_t)h * dv;
-    auto merged = [&](int col) {      // called by all lanes together (the weights travel by shuffle); col may lie beyond dv
+    __syncthreads();
+    const int col = threadIdx.x;
+    if (col < dv) {
         float v = 0.0f;
-        const bool in = col < dv;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            for (int s0 = 0; s0 < 32 && 32 * j + s0 < nsplit; ++s0) {
-                const float w = __shfl_sync(0xffffffffu, wgt[j], s0);
-                if (in) v = fmaf(w, rec[(size_t)(32 * j + s0) * (dv + 2) + 2 + col], v);
-            }
-        }
-        for (int s = 128; s < nsplit; ++s) {
-            const float ms = rec[(size_t)s * (dv + 2)];
-            if (in && ms != -INFINITY) v = fmaf(expf(ms - mx), rec[(size_t)s * (dv + 2) + 2 + col], v);
-        }
-        return v * inv_den;
-    };
+#pragma unroll 4
+        for (int s = 0; s < nsplit; ++s) v = fmaf(s_w[s], rec[(size_t)s * (dv + 2) + 2 + col], v);
+        s_o[col] = v;
+    }
+    __syncthreads();
+    const float gv = gate ? seq_sigmoid(gate[(size_t)t * ldg + h]) : 1.0f;
+    float* orow = out + (size_t)t * ldo + (size_t)h * dv;
     if (!vfreq) {
-        for (int c0 = 0; c0 < dv; c0 += 32) {
-            const float v = merged(c0 + lane);
-            if (c0 + lane < dv) orow[c0 + lane] = v * gv;
-        }
+        if (col < dv) orow[col] = s_o[col] * gv;
         return;
     }
-    const int half = dv / 2;
-    for (int m0 = 0; m0 < half; m0 += 32) {
-        const int mi = m0 + lane;
-        const bool in = mi < half;
+    const int half = dv / 2, mi = threadIdx.x;
+    if (mi < half) {
         const int ia = layout == 0 ? 2 * mi : mi, ib = layout == 0 ? 2 * mi + 1 : mi + half;
-        const float u = merged(in ? ia : dv), v = merged(in ? ib : dv);
-        if (in) {
-            float sn, cs;
-            seq_angle(pos, vfreq[mi], &sn, &cs);
-            orow[ia] = (u * cs + v * sn) * gv;    // rotation by the negative angle
-            orow[ib] = (v * cs - u * sn) * gv;
-        }
+        const float u = s_o[ia], v = s_o[ib];
+        float sn, cs;
+        seq_angle(b.tok_pos[t], vfreq[mi], &sn, &cs);
+        orow[ia] = (u * cs + v * sn) * gv;    // rotation by the negative angle
+        orow[ib] = (v * cs - u * sn) * gv;
     }
 }
 
@@ -442,10 +424,13 @@ __global__ void seq_rotary_kv_kernel(sllm_seq_batch b, float* __restrict__ q, in
                                      const double* __restrict__ vfreq, int layout, KV* __restrict__ k_pool, KV* __restrict__ v_pool) {
     const int t = blockIdx.x, posi = b.tok_pos[t], slot = b.tok_slot[t];
     const int pos = posi;
+    // gridDim.y CTAs share a token: CTA y takes the work items y, y + gridDim.y, ... of each of the three loops (single tokens would
+    // otherwise leave one CTA with every head's sines and cosines)
+    const int tid = blockIdx.y * blockDim.x + threadIdx.x, nthr = gridDim.y * blockDim.x;
     const int page = b.block_table[(size_t)slot * b.max_pages + posi / b.page_len], in_page = posi % b.page_len;
     const int rd = 2 * n_freq, rhalf = n_freq;
     // q: heads * (dk/2 rounded up) work items; pairs beyond the rotary dimensions pass unchanged (they stay in place)
-    for (int i = threadIdx.x; i < heads * n_freq; i += blockDim.x) {
+    for (int i = tid; i < heads * n_freq; i += nthr) {
         const int h = i / n_freq, mi = i % n_freq;
         const int ia = layout == 0 ? 2 * mi : mi, ib = layout == 0 ? 2 * mi + 1 : mi + rhalf;
         float sn, cs;
@@ -457,7 +442,7 @@ __global__ void seq_rotary_kv_kernel(sllm_seq_batch b, float* __restrict__ q, in
         qh[ia] = u * cs - w * sn;
         qh[ib] = w * cs + u * sn;
     }
-    for (int i = threadIdx.x; i < kv_heads * dk; i += blockDim.x) {
+    for (int i = tid; i < kv_heads * dk; i += nthr) {
         const int g = i / dk, c = i % dk;
         const float* kh = k + (size_t)t * ldk + (size_t)g * dk;
         float val = kh[c];
@@ -474,7 +459,7 @@ __global__ void seq_rotary_kv_kernel(sllm_seq_batch b, float* __restrict__ q, in
         seq_st(k_pool, seq_pool_row(page, kv_heads, g, b.page_len, in_page, dk) + c, val);
     }
     const int vhalf = dv / 2;
-    for (int i = threadIdx.x; i < kv_heads * dv; i += blockDim.x) {
+    for (int i = tid; i < kv_heads * dv; i += nthr) {
         const int g = i / dv, c = i % dv;
         const float* vh = v + (size_t)t * ldv + (size_t)g * dv;
         float val = vh[c];
@@ -511,11 +496,14 @@ int sllm_seq_rotary_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t h
     SLLM_REQUIRE(!vfreq || dv % 2 == 0, SLLM_EINVAL, "seq_rotary_kv: rotated values need an even width");
     SLLM_REQUIRE(layout == 0 || layout == 1, SLLM_EINVAL, "seq_rotary_kv: layout 0 (interleaved) or 1 (halves)");
     SLLM_REQUIRE(kv_dtype == SLLM_F32 || kv_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_rotary_kv: fp32 or bf16 pools");
+    // enough CTAs per token that a step of few tokens still spreads its sines and cosines over the machine
+    const int work = std::max(heads * n_freq, kv_heads * std::max(dk, dv));
+    const dim3 rgrid(b->T, std::max(1, std::min((work + 127) / 128, b->T >= 64 ? 1 : 16)));
     if (kv_dtype == SLLM_F32)
-        seq_rotary_kv_kernel<float><<<b->T, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, freq, n_freq, magnitude, vfreq,
+        seq_rotary_kv_kernel<float><<<rgrid, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, freq, n_freq, magnitude, vfreq,
                                                                          layout, (float*)k_pool, (float*)v_pool);
     else
-        seq_rotary_kv_kernel<uint16_t><<<b->T, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, freq, n_freq, magnitude,
+        seq_rotary_kv_kernel<uint16_t><<<rgrid, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, freq, n_freq, magnitude,
                                                                             vfreq, layout, (uint16_t*)k_pool, (uint16_t*)v_pool);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
@@ -566,8 +554,10 @@ int sllm_seq_attention_finish(const sllm_seq_batch* b, const float* ws, int32_t 
                               const float* gate, int32_t ldg, float* out, int32_t ldo, sllm_stream_t stream) {
     if (int rc = check_batch(b, "seq_attention_finish")) return rc;
     SLLM_REQUIRE(ws && out && nsplit >= 1 && heads > 0 && dv > 0 && (!vfreq || dv % 2 == 0), SLLM_EINVAL, "seq_attention_finish: bad argument");
-    const int items = b->T * heads;
-    seq_attention_finish_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(*b, ws, nsplit, heads, dv, vfreq, layout, gate, ldg, out, ldo);
+    SLLM_REQUIRE(dv <= 1024 && nsplit <= 8192, SLLM_ENOTSUP, "seq_attention_finish: value width %d / %d shares beyond what one CTA merges", dv, nsplit);
+    const int threads = std::max(32, (dv + 31) / 32 * 32);
+    seq_attention_finish_kernel<<<b->T * heads, threads, (size_t)(nsplit + dv) * sizeof(float), as_stream(stream)>>>(*b, ws, nsplit, heads, dv, vfreq, layout, gate,
+                                                                                                                  ldg, out, ldo);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
