@@ -65,8 +65,15 @@ __global__ void seq_hyper_write_read_kernel(float* __restrict__ x, int streams, 
                                             const float* __restrict__ y_in, const float* __restrict__ coef, const float* __restrict__ norm_w, int groups,
                                             float eps, float* __restrict__ y_out) {
     __shared__ float red[33];
+    __shared__ float s_mix[kMaxStreams * kMaxStreams], s_outc[kMaxStreams], s_coef[kMaxStreams];   // the small matrices once per CTA, not per element
     const int t = blockIdx.x, g = blockIdx.y, n = d / groups, j0 = g * n;
     const size_t plane = (size_t)T * d;
+    if (threadIdx.x < streams * streams) s_mix[threadIdx.x] = mix ? mix[threadIdx.x] : ((int)threadIdx.x / streams == (int)threadIdx.x % streams ? 1.0f : 0.0f);
+    if (threadIdx.x < streams) {
+        s_outc[threadIdx.x] = outc ? outc[threadIdx.x] : 1.0f;
+        s_coef[threadIdx.x] = coef ? coef[threadIdx.x] : 1.0f;
+    }
+    __syncthreads();
     float ss = 0.0f;
     for (int j = threadIdx.x; j < n; j += blockDim.x) {
         const size_t i = (size_t)t * d + j0 + j;
@@ -78,13 +85,13 @@ __global__ void seq_hyper_write_read_kernel(float* __restrict__ x, int streams, 
             float v;
             if (mix) {
                 v = 0.0f;
-                for (int s = 0; s < streams; ++s) v = fmaf(mix[s * streams + to], old[s], v);
+                for (int s = 0; s < streams; ++s) v = fmaf(s_mix[s * streams + to], old[s], v);
             } else {
                 v = old[to];
             }
-            v = fmaf(outc ? outc[to] : 1.0f, yv, v);
+            v = fmaf(s_outc[to], yv, v);
             x[(size_t)to * plane + i] = v;
-            u = fmaf(coef ? coef[to] : 1.0f, v, u);
+            u = fmaf(s_coef[to], v, u);
         }
         y_out[i] = u;
         ss = fmaf(u, u, ss);
@@ -198,7 +205,7 @@ int sllm_seq_hyper_write_read(float* x, int32_t streams, int32_t T, int32_t d, c
 
 int sllm_seq_polynorm(const float* z, int32_t ldz, const float* coef, float eps, float* out, int32_t ldo, int32_t T, int32_t n, sllm_stream_t stream) {
     SLLM_REQUIRE(z && coef && out && T > 0 && n > 0 && ldz >= n && ldo >= n, SLLM_EINVAL, "seq_polynorm: bad argument");
-    seq_polynorm_kernel<<<T, n >= 2048 ? 512 : 256, 0, as_stream(stream)>>>(z, ldz, coef, eps, out, ldo, n);
+    seq_polynorm_kernel<<<T, n >= 8192 ? 1024 : (n >= 2048 ? 512 : 256), 0, as_stream(stream)>>>(z, ldz, coef, eps, out, ldo, n);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
