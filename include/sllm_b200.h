@@ -413,9 +413,9 @@ typedef struct {
     const int32_t* seg_tile0;    /* [nseg] running count of tiles of the segments before this one (tile ids in segment order) */
 } sllm_seq_batch;
 
-/* out[s][t][:] = table[ids[t]][:] for every stream s (a model with one residual stream passes streams = 1) */
-int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32_t vocab, int32_t d, int32_t streams, float* out,
-                   int32_t T, sllm_stream_t stream);
+/* out[s][t][:] = table[ids[t]][:] * scale for every stream s (a model with one residual stream passes streams = 1) */
+int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32_t vocab, int32_t d, int32_t streams, float scale,
+                   float* out, int32_t T, sllm_stream_t stream);
 /* u = sum_s coef[s] * x[s] (coef NULL = all ones), then, if norm_w is given, the RMS norm in `groups` equal consecutive parts:
  * every part divided by sqrt(mean(part^2) + eps), the whole multiplied by norm_w. x: [streams][T][d], y: [T][d]. */
 int sllm_seq_hyper_read(const float* x, int32_t streams, int32_t T, int32_t d, const float* coef, const float* norm_w, int32_t groups,
@@ -447,16 +447,52 @@ int sllm_seq_gather_rows(const float* x, int32_t ldx, const int32_t* rows, int32
 int sllm_seq_rotary_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk,
                        int32_t kv_heads, const float* v, int32_t ldv, int32_t dv, const double* freq, int32_t n_freq, float magnitude,
                        const double* vfreq, int32_t layout, void* k_pool, void* v_pool, int32_t kv_dtype, sllm_stream_t stream);
+/* What an attention launch may ask for beyond plain causal softmax (NULL = none of it). */
+typedef struct {
+    int32_t window;          /* > 0: query i sees key j <= i only when i - j < window or j < keep_first; 0 = every key before it */
+    int32_t keep_first;      /* the first positions of a sequence stay visible behind the window, at their true positions */
+    float softcap;           /* > 0: score <- softcap * tanh(score / softcap), after the scale */
+    const float* slopes;     /* [heads] or NULL: score <- score - slopes[h] * (i - j), after the cap */
+    int32_t values_in_keys;  /* != 0: a value row is the first dv columns of the key row (one pool; v_pool is not read) */
+} sllm_seq_attn_opts;
 /* Causal softmax attention of every token over positions 0..pos of its own sequence: score = (q . k) * scale, query head h reads
  * key/value head h / (heads / kv_heads). Keys are visited in tiles of 32, cut into nsplit interleaved shares; the partial results
- * (running maximum, sum, unnormalised output) go to ws: [T][heads][nsplit][dv + 2] floats. */
+ * (running maximum, sum, unnormalised output) go to ws: [T][heads][nsplit][dv + 2] floats. Tiles that a window hides from all queries
+ * of a work item are not loaded. */
 int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t kv_heads, int32_t dk, int32_t dv,
                        float scale, const void* k_pool, const void* v_pool, int32_t kv_dtype, int32_t nsplit, float* ws,
-                       sllm_stream_t stream);
-/* Merges the shares, normalises, turns every head's output back by -pos * vfreq[m] (vfreq NULL = not), multiplies head h by
- * sigmoid(gate[t][h]) (gate NULL = not) and stores out[t][h*dv ..]. */
+                       const sllm_seq_attn_opts* opts, sllm_stream_t stream);
+/* Merges the shares, normalises (sink [heads] or NULL: the denominator of head h also holds exp(sink[h]), a term without key or value),
+ * turns every head's output back by -pos * vfreq[m] (vfreq NULL = not), multiplies head h by sigmoid(gate[t][h]) (gate NULL = not) and
+ * stores out[t][h*dv ..]. */
 int sllm_seq_attention_finish(const sllm_seq_batch* b, const float* ws, int32_t nsplit, int32_t heads, int32_t dv, const double* vfreq,
-                              int32_t layout, const float* gate, int32_t ldg, float* out, int32_t ldo, sllm_stream_t stream);
+                              int32_t layout, const float* gate, int32_t ldg, const float* sink, float* out, int32_t ldo,
+                              sllm_stream_t stream);
+/* Heads scaled to unit root mean square and the cache write, for mixers without rotation: bit 0 of `unit` = every query head of q (in
+ * place), bit 1 = every key head, bit 2 = every value head is divided by sqrt(mean(head^2) + eps). share 1: the values (after the
+ * division) are also kept in v_shared [T][kv_heads*dv]; share 2: v <- (1 - lambda) * v + lambda * v_shared (what an earlier layer kept
+ * for the same tokens). k and v go to their pools at (page of pos, kv head, pos % page_len). */
+int sllm_seq_unit_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk,
+                     int32_t kv_heads, const float* v, int32_t ldv, int32_t dv, float eps, int32_t unit, float* v_shared, int32_t share,
+                     float lambda, void* k_pool, void* v_pool, int32_t kv_dtype, sllm_stream_t stream);
+/* Latent attention's cache write: low [T][rank + dr] is one token's low-rank row; its first `rank` entries, RMS-normed with norm_w, and
+ * its last dr entries, the first 2*n_freq of them rotated by pos * freq[i] (interleaved pairs, angles in double), form the pool row
+ * [pages][1][page_len][rank + dr]. q [T][heads][dn + dr]: the dr-part of every head is rotated the same way and stored at
+ * q_out[t][h][rank ..] (q_out rows of heads * (rank + dr); the first `rank` columns of a head belong to the absorbed query). */
+int sllm_seq_latent_kv(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t dn, int32_t dr, const float* low,
+                       int32_t ldlow, int32_t rank, const float* norm_w, float eps, const double* freq, int32_t n_freq, float* q_out,
+                       int32_t ldqo, void* pool, int32_t kv_dtype, sllm_stream_t stream);
+/* y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + bias per row (bias NULL = none) */
+int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, int32_t T,
+                       int32_t d, sllm_stream_t stream);
+/* Depth-weighted average: hist [n_prev + 1 ..][T][d] holds the embedding output and every earlier layer's own result. Stores this
+ * layer's result hist[n_prev] = x + y, replaces x by sum_{j <= n_prev} coef[j] * hist[j], and, with norm_w, writes the layer norm
+ * (norm_w, norm_b, eps) of the new x to h. */
+int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev, const float* coef, const float* norm_w,
+                           const float* norm_b, float eps, float* h, int32_t T, int32_t d, sllm_stream_t stream);
+/* out = g * sigmoid(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), element-wise over [T][n] */
+int sllm_seq_clamped_glu(const float* gate, int32_t ldg, const float* up, int32_t ldu, float limit, float alpha, float* out, int32_t ldo,
+                         int32_t T, int32_t n, sllm_stream_t stream);
 /* Causal convolution per channel over each sequence: u[t][c] = cb[c] + sum_k w[c][k] * x[t - (taps-1-k)][c]; inputs before the segment
  * come from tail[slot][taps-1][channels] (zeros for a new sequence). The tail is NOT updated here (sllm_seq_rglru_scan does it). */
 int sllm_seq_conv(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* cb,

@@ -123,9 +123,14 @@ class SeqBatch(C.Structure):
                 ("seg_pos0", _P), ("block_table", _P), ("max_pages", _I), ("page_len", _I), ("n_qtiles", _I), ("qt_seg", _P), ("qt_off", _P), ("seg_tile0", _P)]
 
 
+class SeqAttnOpts(C.Structure):
+    """sllm_seq_attn_opts: window / kept first positions / score cap / distance slopes / values inside the key rows."""
+    _fields_ = [("window", _I), ("keep_first", _I), ("softcap", _F), ("slopes", _P), ("values_in_keys", _I)]
+
+
 _B = C.POINTER(SeqBatch)
 SIGNATURES.update({
-    "sllm_seq_embed": (C.c_int, [_P, _P, _I, _I, _I, _I, _P, _I, _P]),
+    "sllm_seq_embed": (C.c_int, [_P, _P, _I, _I, _I, _I, _F, _P, _I, _P]),
     "sllm_seq_hyper_read": (C.c_int, [_P, _I, _I, _I, _P, _P, _I, _F, _P, _P]),
     "sllm_seq_hyper_write": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "sllm_seq_hyper_write_read": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _F, _P, _P]),
@@ -133,8 +138,13 @@ SIGNATURES.update({
     "sllm_seq_polynorm": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "sllm_seq_gather_rows": (C.c_int, [_P, _I, _P, _I, _I, _P, _P]),
     "sllm_seq_rotary_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _F, _P, _I, _P, _P, _I, _P]),
-    "sllm_seq_attention": (C.c_int, [_B, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _P, _P]),
-    "sllm_seq_attention_finish": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _P, _I, _P, _I, _P]),
+    "sllm_seq_attention": (C.c_int, [_B, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _P, C.POINTER(SeqAttnOpts), _P]),
+    "sllm_seq_attention_finish": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _P]),
+    "sllm_seq_unit_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _F, _P, _P, _I, _P]),
+    "sllm_seq_latent_kv": (C.c_int, [_B, _P, _I, _I, _I, _I, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P]),
+    "sllm_seq_layernorm": (C.c_int, [_P, _I, _P, _P, _F, _P, _I, _I, _I, _P]),
+    "sllm_seq_depth_average": (C.c_int, [_P, _P, _P, _I, _P, _P, _P, _F, _P, _I, _I, _P]),
+    "sllm_seq_clamped_glu": (C.c_int, [_P, _I, _P, _I, _F, _F, _P, _I, _I, _I, _P]),
     "sllm_seq_conv": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "sllm_seq_rglru_scan": (C.c_int, [_B, _P, _I, _P, _P, _I, _P, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _I, _P, _P]),
     "sllm_seq_gla_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _P]),

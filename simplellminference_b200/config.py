@@ -157,7 +157,107 @@ class MunazenConfig:
                 + list(range(self.loop_stop, len(self.layers))))
 
 
-CONFIG_READERS = {"Munazen": MunazenConfig.from_dict}
+@dataclass(frozen=True)
+class WindowMask:
+    """Which earlier positions a query sees: ``size`` None = all of them; else the last ``size`` (itself included) and, whatever the
+    distance, the first ``keep_first`` positions of the sequence."""
+    size: int | None = None
+    keep_first: int = 0
+
+    @staticmethod
+    def from_dict(m: dict | None) -> "WindowMask":
+        m = m or {}
+        size = m.get("size")
+        return WindowMask(int(size) if size else None, int(m.get("keep_first") or 0))
+
+
+@dataclass(frozen=True)
+class CappedAttentionConfig:
+    """Softmax attention without rotation: unit-rms heads, capped scores, a slope per head on the distance, a window that keeps the first
+    positions, values optionally blended with those of the first such layer."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    softcap: float          # 0 = no cap
+    mask: WindowMask
+    v_mix: bool
+
+
+@dataclass(frozen=True)
+class LatentAttentionConfig:
+    """Attention whose keys and values are expanded from one cached latent vector per token (``kv_rank``) plus one rotated key part
+    (``rot_dim``) shared by the heads; ``dim`` is the unrotated query / key width of a head."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: RotaryConfig
+    mask: WindowMask
+
+
+@dataclass(frozen=True)
+class ClampedGluConfig:
+    ff: int
+    limit: float
+
+
+@dataclass(frozen=True)
+class SopetarLayerConfig:
+    type: str                                    # "attention" | "latent_attention"
+    mixer: object                                # CappedAttentionConfig | LatentAttentionConfig
+    mlp: ClampedGluConfig | None = None          # None = the layer has no feed-forward
+
+
+@dataclass(frozen=True)
+class SopetarConfig:
+    """The Sopetar design: parallel layers (one layer norm feeds the mixer and the feed-forward), a depth-weighted average of all earlier
+    layers' results between layers. Every size and every constant that may differ between its models comes from config.json."""
+    architecture: str
+    vocab: int
+    width: int
+    embedding_scale: float
+    norm_eps: float
+    layers: tuple
+
+    @staticmethod
+    def from_dict(c: dict) -> "SopetarConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            m, mlp = l["mixer"], l.get("mlp")
+            ff = None
+            if mlp is not None:
+                if mlp.get("kind", "dense") != "dense":
+                    raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")
+                ff = ClampedGluConfig(int(mlp["ff"]), float(mlp["limit"]))
+            mask = WindowMask.from_dict(m.get("mask"))
+            if l["type"] == "attention":
+                heads = int(m["heads"])
+                kv_heads = int(m.get("kv_heads") or heads)
+                if heads % kv_heads:
+                    raise ValueError(f"layer {i}: {heads} query heads do not divide over {kv_heads} key/value heads")
+                mixer = CappedAttentionConfig(heads, kv_heads, int(m["dim"]), int(m["vdim"]), float(m["scale"]), float(m.get("softcap") or 0.0), mask,
+                                              bool(m.get("v_mix")))
+            elif l["type"] == "latent_attention":
+                rot = m["rot"]
+                mixer = LatentAttentionConfig(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"]),
+                                              RotaryConfig(int(rot["dims"]), float(rot["base"]), None), mask)
+                if mixer.rot.dims > mixer.rot_dim or mixer.rot.dims % 2:
+                    raise ValueError(f"layer {i}: {mixer.rot.dims} rotary dimensions do not fit a rotated part of {mixer.rot_dim}")
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {l['type']!r}")
+            layers.append(SopetarLayerConfig(l["type"], mixer, ff))
+        shared = [l.mixer for l in layers if l.type == "attention" and l.mixer.v_mix]
+        if any((m.kv_heads, m.vdim) != (shared[0].kv_heads, shared[0].vdim) for m in shared):
+            raise ValueError("layers that blend their values with the first such layer's need the same key/value heads and value width")
+        return SopetarConfig(c["architecture"], int(c["vocab"]), int(c["width"]), float((c.get("embedding") or {}).get("scale", 1.0)),
+                             float((c.get("norm") or {}).get("eps", 1e-6)), tuple(layers))
+
+
+CONFIG_READERS = {"Munazen": MunazenConfig.from_dict, "Sopetar": SopetarConfig.from_dict}
 
 
 def read_model_config(model_dir: str):

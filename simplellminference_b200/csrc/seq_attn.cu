@@ -2,29 +2,25 @@
 // one launch: rotary positions on q / k (partial, interleaved or half-split pairs, scaled frequencies arrive as a table), values rotated by
 // their own position before they are cached and turned back by the query's position afterwards, key and value heads of different widths,
 // grouped query heads, a sigmoid gate per head. Scores, softmax weights and the weighted sum are fp32 whatever the cache holds.
+// Options of a launch (sllm_seq_attn_opts): a sliding window that keeps the first positions of a sequence visible (key tiles that no query
+// of the CTA can see are never loaded), scores capped by cap * tanh(score / cap), a charge per position of distance with one slope per
+// head, values that are the leading columns of the key rows (one pool holds both: latent attention in its absorbed form), and in the
+// merge one more term exp(sink) per head in the softmax's denominator.
 //
 // seq_attention_kernel: CTA = (tile of up to 32 consecutive queries of one segment, query head, share of the key tiles), 8 warps x 4
 // queries. A tile of 32 keys and values of the head's kv head is staged in shared memory (fp32); a lane owns one key for the scores
 // (16-byte shared loads, rows padded by 4 floats: conflict-free) and dv/32 output columns for the weighted sum; online softmax per query
 // with warp reductions. The key tiles are dealt to `nsplit` CTAs in turn (long contexts with few queries: decode), every CTA leaves
 // (max, sum, unnormalised output) and seq_attention_finish_kernel merges them.
+#include <climits>
+
 #include "seq_common.cuh"
 
 namespace sllm {
 
 extern int g_tune_seq_attn_mma;   // runtime.cu: 1 (default) = tensor-core attention body where it applies, 0 = always the fp32 body
 
-// cos and sin of pos * freq. The product is formed and reduced in double: at position 1000 an fp32 product is already off by up to
-// 3e-5 rad, five hundred times the rounding of everything else in the layer, and the error would grow with the position.
-__device__ __forceinline__ void seq_angle(int pos, double freq, float* sn, float* cs) {
-    double s, c;
-    sincos((double)pos * freq, &s, &c);
-    *sn = (float)s;
-    *cs = (float)c;
-}
-
 constexpr int kBQ = 32, kBK = 32, kQW = 4;   // queries per CTA, keys per tile, queries per warp
-constexpr int kMaxDvChunks = 8;              // dv <= 256
 
 struct AttnArgs {
     sllm_seq_batch b;
@@ -32,15 +28,43 @@ struct AttnArgs {
     const void *k_pool, *v_pool;
     int nsplit; float* ws;
     int by_head;   // fp32 body, steps of single tokens: a CTA's "queries" are the query heads of ONE kv head at one token (they share its tiles)
+    int window, keep_first;   // query i sees key j <= i when i - j < window or j < keep_first (window INT_MAX = everything before it)
+    float softcap;            // > 0: score <- softcap * tanh(score / softcap)
+    const float* slopes;      // [heads] or NULL: score <- score - slopes[h] * (i - j)
+    int v_in_k;               // values = the first dv columns of the key rows (v_pool unused)
 };
 
-template <typename KV>
+// The key tiles a CTA whose queries lie at positions first .. last has to visit: the tiles of the kept first positions, then the tiles
+// from the one that holds the oldest key inside the first query's window up to the last query's own tile.
+struct TileList {
+    int n_keep, lo, n;
+    __device__ __forceinline__ TileList(int first, int last, int window, int keep_first, int tile) {
+        const int nkt = last / tile + 1;
+        const int oldest = window > first ? 0 : first - window + 1;
+        lo = oldest / tile;
+        n_keep = min(lo, (min(keep_first, oldest) + tile - 1) / tile);
+        n = n_keep + nkt - lo;
+    }
+    __device__ __forceinline__ int tile_of(int idx) const { return idx < n_keep ? idx : lo + idx - n_keep; }
+};
+
+__device__ __forceinline__ float seq_score(float dot, float scale, float softcap, float slope, int qpos, int key) {
+    float sc = dot * scale;
+    if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
+    return sc - slope * (float)(qpos - key);
+}
+__device__ __forceinline__ bool seq_sees(int qpos, int key, int window, int keep_first) {
+    return key <= qpos && (qpos - key < window || key < keep_first);
+}
+
+template <typename KV, int kMaxDvChunks>   // dv <= 32 * kMaxDvChunks
 __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     extern __shared__ __align__(16) float sm[];
     const int dk = p.dk, dv = p.dv, dkp = ((dk + 3) & ~3) + 4;   // padded row of q / k in floats
     float* sq = sm;                      // [kBQ][dkp]
     float* sk = sq + kBQ * dkp;          // [kBK][dkp]
-    float* sv = sk + kBK * dkp;          // [kBK][dv]
+    float* sv = p.v_in_k ? sk : sk + kBK * dkp;   // [kBK][dv], or the key rows themselves
+    const int ldsv = p.v_in_k ? dkp : dv;
     const sllm_seq_batch& b = p.b;
     const int qt = blockIdx.x, split = blockIdx.z;
     const int seg = b.qt_seg[qt], off = b.qt_off[qt];
@@ -68,15 +92,19 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
 #pragma unroll
         for (int c = 0; c < kMaxDvChunks; ++c) acc[i][c] = 0.0f;
     }
-    const int last_pos = row_pos(nq - 1), nkt = last_pos / kBK + 1;
-    for (int kt = split; kt < nkt; kt += p.nsplit) {
-        const int j0 = kt * kBK;
+    float slope[kQW];
+#pragma unroll
+    for (int i = 0; i < kQW; ++i) slope[i] = (p.slopes && warp * kQW + i < nq) ? p.slopes[row_head(warp * kQW + i)] : 0.0f;
+    const int last_pos = row_pos(nq - 1);
+    const TileList tiles(row_pos(0), last_pos, p.window, p.keep_first, kBK);
+    for (int idx = split; idx < tiles.n; idx += p.nsplit) {
+        const int j0 = tiles.tile_of(idx) * kBK;
         const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
         const int valid = min(kBK, last_pos + 1 - j0);   // keys of this tile that exist
         __syncthreads();
         const size_t krow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dv);
         constexpr int E = 16 / sizeof(KV);   // elements per 16-byte load
-        if (dk % E == 0 && dv % E == 0) {
+        if (dk % E == 0 && (dv % E == 0 || p.v_in_k)) {
             // the tile's rows are consecutive in the pool: 16-byte loads, rows beyond `valid` zero-filled (dk is a multiple of 4 here, so the
             // padding columns of a row are never read)
             const int kgroups = dk / E, vgroups = dv / E;
@@ -87,7 +115,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
 #pragma unroll
                 for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(sk + r * dkp + c + e) = make_float4(vals[e], vals[e + 1], vals[e + 2], vals[e + 3]);
             }
-            for (int i = threadIdx.x; i < kBK * vgroups; i += blockDim.x) {
+            for (int i = threadIdx.x; i < (p.v_in_k ? 0 : kBK * vgroups); i += blockDim.x) {
                 const int r = i / vgroups;
                 float vals[E];
                 seq_ld16(vp + vrow + (size_t)i * E, r < valid, vals);
@@ -99,7 +127,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
                 const int r = i / dkp, c = i % dkp;
                 sk[i] = (r < valid && c < dk) ? seq_ld(kp, krow + (size_t)r * dk + c) : 0.0f;
             }
-            for (int i = threadIdx.x; i < kBK * dv; i += blockDim.x) {
+            for (int i = threadIdx.x; i < (p.v_in_k ? 0 : kBK * dv); i += blockDim.x) {
                 const int r = i / dv;
                 sv[i] = r < valid ? seq_ld(vp, vrow + i) : 0.0f;
             }
@@ -123,8 +151,8 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
 #pragma unroll
         for (int i = 0; i < kQW; ++i) {
             const int qi = warp * kQW + i;
-            const bool see = qi < nq && (j0 + lane) <= row_pos(qi);
-            const float sc = see ? s[i] * p.scale : -INFINITY;
+            const bool see = qi < nq && seq_sees(row_pos(qi), j0 + lane, p.window, p.keep_first);
+            const float sc = see ? seq_score(s[i], p.scale, p.softcap, slope[i], row_pos(qi), j0 + lane) : -INFINITY;
             const float mn = fmaxf(m[i], warp_max(sc));
             const float corr = (mn == -INFINITY) ? 1.0f : expf(m[i] - mn);   // m = -inf: nothing accumulated yet, expf(-inf) = 0 is right too
             pw[i] = see ? expf(sc - mn) : 0.0f;
@@ -141,7 +169,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
             for (int c = 0; c < kMaxDvChunks; ++c) {
                 if (c * 32 < dv) {
                     const int col = c * 32 + lane;
-                    const float vv = col < dv ? sv[jj * dv + col] : 0.0f;
+                    const float vv = col < dv ? sv[jj * ldsv + col] : 0.0f;
 #pragma unroll
                     for (int i = 0; i < kQW; ++i) acc[i][c] = fmaf(pj[i], vv, acc[i][c]);
                 }
@@ -187,7 +215,6 @@ __device__ __forceinline__ void split_bf16(float p0, float p1, uint32_t* hi, uin
     *lo = pack_bf16(p0 - __uint_as_float((uint32_t)h0 << 16), p1 - __uint_as_float((uint32_t)h1 << 16));
 }
 
-constexpr int kMmaDkSteps = 8, kMmaDvTiles = 16;   // dk <= 128 (multiple of 16), dv <= 128 (multiple of 8)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // 16 bytes global -> shared without passing through registers; bytes = 0 writes zeros and reads nothing
@@ -198,10 +225,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+template <int kMmaDkSteps, int kMmaDvTiles>   // dk <= 16 * kMmaDkSteps (multiple of 16), dv <= 8 * kMmaDvTiles (multiple of 8)
 __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     extern __shared__ __align__(16) uint16_t smh[];
-    const int dk = p.dk, dv = p.dv, ldk = dk + 8, ldvr = dv + 8;
-    const int stage_elems = kBK * (ldk + ldvr);   // one stage: K rows [kBK][ldk], then V rows [kBK][ldvr]
+    const int dk = p.dk, dv = p.dv, ldk = dk + 8, ldvr = p.v_in_k ? ldk : dv + 8;
+    const int stage_elems = p.v_in_k ? kBK * ldk : kBK * (ldk + ldvr);   // one stage: K rows [kBK][ldk], then V rows [kBK][ldvr] unless the key rows hold them
     const sllm_seq_batch& b = p.b;
     const int qt = blockIdx.x, split = blockIdx.z;
     const int seg = b.qt_seg[qt], off = b.qt_off[qt];
@@ -215,7 +243,9 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     const uint16_t* vp = reinterpret_cast<const uint16_t*>(p.v_pool);
     const int r0 = wq * 16 + g, r1 = r0 + 8;           // this thread's two query rows inside the tile
     const bool ok0 = r0 < nq, ok1 = r1 < nq;
-    const int last_pos = pos0 + nq - 1, nkt = last_pos / kBK + 1;
+    const int last_pos = pos0 + nq - 1;
+    const TileList tiles(pos0, last_pos, p.window, p.keep_first, kBK);
+    const float slope = p.slopes ? p.slopes[h] : 0.0f;
 
     // tile kt of the sequence -> stage `st` of shared memory, asynchronously (rows beyond the last position are zero-filled)
     auto issue = [&](int kt, int st) {
@@ -230,13 +260,13 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
             const int r = i / (dk / 8), cc = (i % (dk / 8)) * 8;
             cp_async16(sK + r * ldk + cc, r < valid ? ksrc + (size_t)r * dk + cc : ksrc, r < valid ? 16 : 0);
         }
-        for (int i = threadIdx.x; i < kBK * (dv / 8); i += blockDim.x) {
+        for (int i = threadIdx.x; i < (p.v_in_k ? 0 : kBK * (dv / 8)); i += blockDim.x) {
             const int r = i / (dv / 8), cc = (i % (dv / 8)) * 8;
             cp_async16(sV + r * ldvr + cc, r < valid ? vsrc + (size_t)r * dv + cc : vsrc, r < valid ? 16 : 0);
         }
         cp_async_commit();
     };
-    if (split < nkt) issue(split, 0);
+    if (split < tiles.n) issue(tiles.tile_of(split), 0);
 
     uint32_t qf[kMmaDkSteps][4];
 #pragma unroll
@@ -259,17 +289,17 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     const int warp_last = pos0 + min(nq - 1, wq * 16 + 15);
     const bool warp_live = wq * 16 < nq;
     int it = 0;
-    for (int kt = split; kt < nkt; kt += p.nsplit, ++it) {
-        const int j0 = kt * kBK, st = it & 1;
-        if (kt + p.nsplit < nkt) {          // the next tile travels while this one is multiplied
-            issue(kt + p.nsplit, st ^ 1);
+    for (int idx = split; idx < tiles.n; idx += p.nsplit, ++it) {
+        const int j0 = tiles.tile_of(idx) * kBK, st = it & 1;
+        if (idx + p.nsplit < tiles.n) {     // the next tile travels while this one is multiplied
+            issue(tiles.tile_of(idx + p.nsplit), st ^ 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
         const uint16_t* sK = smh + st * stage_elems;
-        const uint16_t* sV = sK + kBK * ldk;
+        const uint16_t* sV = p.v_in_k ? sK : sK + kBK * ldk;
         if (warp_live && j0 <= warp_last) {
         float s[4][4];
 #pragma unroll
@@ -290,8 +320,9 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = j0 + nt * 8 + 2 * c + (e & 1);
-                const bool see = (e < 2) ? (ok0 && key <= pos0 + r0) : (ok1 && key <= pos0 + r1);
-                s[nt][e] = see ? s[nt][e] * p.scale : -INFINITY;
+                const int qpos = pos0 + ((e < 2) ? r0 : r1);
+                const bool see = ((e < 2) ? ok0 : ok1) && seq_sees(qpos, key, p.window, p.keep_first);
+                s[nt][e] = see ? seq_score(s[nt][e], p.scale, p.softcap, slope, qpos, key) : -INFINITY;
             }
             mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
             mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
@@ -370,7 +401,7 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
 // Warp 0 turns the shares' (max, sum) into one weight per share (exp(m_s - max) / total, zero for a share that saw no key); every thread
 // then adds its column over the shares with coalesced loads; pairs meet through shared memory for the rotation.
 __global__ void seq_attention_finish_kernel(sllm_seq_batch b, const float* __restrict__ ws, int nsplit, int heads, int dv, const double* __restrict__ vfreq,
-                                            int layout, const float* __restrict__ gate, int ldg, float* __restrict__ out, int ldo) {
+                                            int layout, const float* __restrict__ gate, int ldg, const float* __restrict__ sink, float* __restrict__ out, int ldo) {
     extern __shared__ float fsm[];
     float* s_w = fsm;            // [nsplit]
     float* s_o = fsm + nsplit;   // [dv]
@@ -380,6 +411,7 @@ __global__ void seq_attention_finish_kernel(sllm_seq_batch b, const float* __res
         float mx = -INFINITY;
         for (int s = lane; s < nsplit; s += 32) mx = fmaxf(mx, rec[(size_t)s * (dv + 2)]);
         mx = warp_max(mx);
+        if (sink) mx = fmaxf(mx, sink[h]);   // the sink is one more term of the denominator: no key, no value
         float den = 0.0f;
         for (int s = lane; s < nsplit; s += 32) {
             const float ms = rec[(size_t)s * (dv + 2)];
@@ -388,6 +420,7 @@ __global__ void seq_attention_finish_kernel(sllm_seq_batch b, const float* __res
             den = fmaf(rec[(size_t)s * (dv + 2) + 1], w, den);
         }
         den = warp_sum(den);
+        if (sink) den += expf(sink[h] - mx);
         const float inv_den = 1.0f / den;
         for (int s = lane; s < nsplit; s += 32) s_w[s] *= inv_den;
     }
@@ -511,25 +544,37 @@ int sllm_seq_rotary_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t h
 }
 
 int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t kv_heads, int32_t dk, int32_t dv, float scale,
-                       const void* k_pool, const void* v_pool, int32_t kv_dtype, int32_t nsplit, float* ws, sllm_stream_t stream) {
+                       const void* k_pool, const void* v_pool, int32_t kv_dtype, int32_t nsplit, float* ws, const sllm_seq_attn_opts* opts,
+                       sllm_stream_t stream) {
     if (int rc = check_batch(b, "seq_attention")) return rc;
-    SLLM_REQUIRE(q && k_pool && v_pool && ws && b->block_table && b->qt_seg && b->qt_off && b->n_qtiles > 0, SLLM_EINVAL, "seq_attention: bad argument");
+    const int v_in_k = opts && opts->values_in_keys;
+    SLLM_REQUIRE(q && k_pool && (v_pool || v_in_k) && ws && b->block_table && b->qt_seg && b->qt_off && b->n_qtiles > 0, SLLM_EINVAL, "seq_attention: bad argument");
     SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0, SLLM_EINVAL, "seq_attention: %d query heads over %d kv heads", heads, kv_heads);
-    SLLM_REQUIRE(dv > 0 && dv <= 32 * kMaxDvChunks, SLLM_ENOTSUP, "seq_attention: value width %d beyond %d", dv, 32 * kMaxDvChunks);
+    SLLM_REQUIRE(dv > 0 && dv <= 512, SLLM_ENOTSUP, "seq_attention: value width %d beyond 512", dv);
+    SLLM_REQUIRE(!v_in_k || dv <= dk, SLLM_EINVAL, "seq_attention: %d value columns inside key rows of %d", dv, dk);
+    SLLM_REQUIRE(!opts || (opts->window >= 0 && opts->keep_first >= 0 && opts->softcap >= 0.0f), SLLM_EINVAL, "seq_attention: bad options");
     SLLM_REQUIRE(b->page_len % kBK == 0, SLLM_ENOTSUP, "seq_attention: pages of a multiple of %d positions", kBK);
     SLLM_REQUIRE(nsplit >= 1 && nsplit <= 65535, SLLM_EINVAL, "seq_attention: nsplit");
     SLLM_REQUIRE(kv_dtype == SLLM_F32 || kv_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_attention: fp32 or bf16 pools");
     const int dkp = ((dk + 3) & ~3) + 4;
-    const size_t smem = ((size_t)(kBQ + kBK) * dkp + (size_t)kBK * dv) * sizeof(float);
+    const size_t smem = ((size_t)(kBQ + kBK) * dkp + (v_in_k ? 0 : (size_t)kBK * dv)) * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes(), SLLM_ENOTSUP, "seq_attention: heads of %d + %d floats need %zu bytes of shared memory", dk, dv, smem);
-    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0};
+    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0, INT_MAX, 0, 0.0f, nullptr, 0};
+    if (opts) {
+        p.window = opts->window > 0 ? opts->window : INT_MAX;
+        p.keep_first = opts->window > 0 ? opts->keep_first : 0;
+        p.softcap = opts->softcap;
+        p.slopes = opts->slopes;
+        p.v_in_k = v_in_k;
+    }
     dim3 grid(b->n_qtiles, heads, nsplit);
     // steps that hold a portion of a prompt, bf16 pools, head widths the fragments take: the tensor-core body
-    if (kv_dtype == SLLM_BF16 && b->T > b->nseg && dk % 16 == 0 && dk <= 16 * kMmaDkSteps && dv % 8 == 0 && dv <= 8 * kMmaDvTiles && g_tune_seq_attn_mma) {
-        const size_t smem_mma = 2 * (size_t)kBK * (dk + 8 + dv + 8) * sizeof(uint16_t);
+    if (kv_dtype == SLLM_BF16 && b->T > b->nseg && dk % 16 == 0 && dk <= 192 && dv % 8 == 0 && dv <= 128 && g_tune_seq_attn_mma) {
+        const size_t smem_mma = 2 * (size_t)kBK * (dk + 8 + (v_in_k ? 0 : dv + 8)) * sizeof(uint16_t);
         const int hpc = (heads / kv_heads) % 2 == 0 ? 2 : 1;   // query heads per CTA
         grid.y = heads / hpc;
-        seq_attention_mma_kernel<<<grid, 64 * hpc, smem_mma, as_stream(stream)>>>(p);
+        if (dk <= 128) seq_attention_mma_kernel<8, 16><<<grid, 64 * hpc, smem_mma, as_stream(stream)>>>(p);
+        else seq_attention_mma_kernel<12, 16><<<grid, 64 * hpc, smem_mma, as_stream(stream)>>>(p);
         ++g_launches;
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;
@@ -538,26 +583,31 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
         p.by_head = 1;
         grid.y = kv_heads;
     }
+    const int chunks = dv <= 128 ? 4 : (dv <= 256 ? 8 : 16);
+#define SLLM_ATTN_LAUNCH(KV, NC)                                                                                                              \
+    do {                                                                                                                                      \
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<KV, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        seq_attention_kernel<KV, NC><<<grid, 256, smem, as_stream(stream)>>>(p);                                                              \
+    } while (0)
     if (kv_dtype == SLLM_F32) {
-        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        seq_attention_kernel<float><<<grid, 256, smem, as_stream(stream)>>>(p);
+        if (chunks == 4) SLLM_ATTN_LAUNCH(float, 4); else if (chunks == 8) SLLM_ATTN_LAUNCH(float, 8); else SLLM_ATTN_LAUNCH(float, 16);
     } else {
-        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_attention_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        seq_attention_kernel<uint16_t><<<grid, 256, smem, as_stream(stream)>>>(p);
+        if (chunks == 4) SLLM_ATTN_LAUNCH(uint16_t, 4); else if (chunks == 8) SLLM_ATTN_LAUNCH(uint16_t, 8); else SLLM_ATTN_LAUNCH(uint16_t, 16);
     }
+#undef SLLM_ATTN_LAUNCH
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
 }
 
 int sllm_seq_attention_finish(const sllm_seq_batch* b, const float* ws, int32_t nsplit, int32_t heads, int32_t dv, const double* vfreq, int32_t layout,
-                              const float* gate, int32_t ldg, float* out, int32_t ldo, sllm_stream_t stream) {
+                              const float* gate, int32_t ldg, const float* sink, float* out, int32_t ldo, sllm_stream_t stream) {
     if (int rc = check_batch(b, "seq_attention_finish")) return rc;
     SLLM_REQUIRE(ws && out && nsplit >= 1 && heads > 0 && dv > 0 && (!vfreq || dv % 2 == 0), SLLM_EINVAL, "seq_attention_finish: bad argument");
     SLLM_REQUIRE(dv <= 1024 && nsplit <= 8192, SLLM_ENOTSUP, "seq_attention_finish: value width %d / %d shares beyond what one CTA merges", dv, nsplit);
     const int threads = std::max(32, (dv + 31) / 32 * 32);
     seq_attention_finish_kernel<<<b->T * heads, threads, (size_t)(nsplit + dv) * sizeof(float), as_stream(stream)>>>(*b, ws, nsplit, heads, dv, vfreq, layout, gate,
-                                                                                                                  ldg, out, ldo);
+                                                                                                                  ldg, sink, out, ldo);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

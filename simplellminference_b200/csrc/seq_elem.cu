@@ -1,17 +1,19 @@
 // csrc/seq_elem.cu — row-wise building blocks of the ragged token batch (sllm_seq_*): embedding into residual streams, the
 // hyper-connection read (weighted sum of the streams + grouped RMS norm) and write (stream mixing + sublayer output), PolyNorm,
-// row gather and the per-head norm with a SiLU gate. Everything here is fp32: norms and the residual sum are never rounded.
+// row gather and the per-head norm with a SiLU gate; layer norm (weight and bias), the depth-weighted average of a model whose layers
+// read a learned mix of ALL earlier layers' results, and a clamped gated-linear-unit activation. Everything here is fp32: norms and the
+// residual sum are never rounded.
 #include "seq_common.cuh"
 
 namespace sllm {
 
 __global__ void seq_embed_kernel(const int32_t* __restrict__ ids, const void* __restrict__ table, int w_dtype, int vocab, int d, int streams,
-                                 float* __restrict__ out, int T) {
+                                 float scale, float* __restrict__ out, int T) {
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        const float v = seq_ldw(table, w_dtype, (size_t)id * d + j);
+        const float v = seq_ldw(table, w_dtype, (size_t)id * d + j) * scale;
         for (int s = 0; s < streams; ++s) out[((size_t)s * T + t) * d + j] = v;
     }
 }
@@ -151,17 +153,75 @@ __global__ void seq_headnorm_gate_kernel(const float* __restrict__ o, int ldo, c
     }
 }
 
+// (row - mean) / sqrt(variance + eps) * w + b of one row that the CTA's threads hold strided; the variance is the mean of the squared
+// deviations (two passes: the mean first), as the definition says
+__device__ __forceinline__ void seq_layernorm_row(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, float eps,
+                                                  float* __restrict__ y, int d, float* red) {
+    float s = 0.0f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) s += x[j];
+    const float mean = block_sum(s, red) / (float)d;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float c = x[j] - mean;
+        ss = fmaf(c, c, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) y[j] = ((x[j] - mean) * inv) * w[j] + (bias ? bias[j] : 0.0f);
+}
+
+__global__ void seq_layernorm_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias, float eps,
+                                     float* __restrict__ y, int ldy, int d) {
+    __shared__ float red[33];
+    seq_layernorm_row(x + (size_t)blockIdx.x * ldx, w, bias, eps, y + (size_t)blockIdx.x * ldy, d, red);
+}
+
+constexpr int kMaxDepth = 256;
+
+// One CTA per token: hist[n_prev] <- x + y (this layer's own result); x <- sum_{j <= n_prev} coef[j] * hist[j]; h <- layer norm of x.
+// A thread re-reads only what it wrote itself until the norm, whose reductions order the rest.
+__global__ void seq_depth_average_kernel(float* __restrict__ x, const float* __restrict__ y, float* __restrict__ hist, int n_prev, const float* __restrict__ coef,
+                                         const float* __restrict__ norm_w, const float* __restrict__ norm_b, float eps, float* __restrict__ h, int T, int d) {
+    __shared__ float red[33];
+    __shared__ float s_coef[kMaxDepth + 1];
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j <= n_prev; j += blockDim.x) s_coef[j] = coef[j];
+    __syncthreads();
+    const size_t plane = (size_t)T * d, row = (size_t)t * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float own = x[row + j] + y[row + j];
+        hist[(size_t)n_prev * plane + row + j] = own;
+        float u = 0.0f;
+        for (int l = 0; l < n_prev; ++l) u = fmaf(s_coef[l], hist[(size_t)l * plane + row + j], u);
+        x[row + j] = fmaf(s_coef[n_prev], own, u);
+    }
+    if (!norm_w) return;
+    __syncthreads();
+    seq_layernorm_row(x + row, norm_w, norm_b, eps, h + row, d, red);
+}
+
+// out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
+__global__ void seq_clamped_glu_kernel(const float* __restrict__ gate, int ldg, const float* __restrict__ up, int ldu, float limit, float alpha,
+                                       float* __restrict__ out, int ldo, int T, int n) {
+    const size_t total = (size_t)T * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / n, j = i % n;
+        const float g = fminf(gate[t * ldg + j], limit);
+        const float u = fminf(fmaxf(up[t * ldu + j], -limit), limit);
+        out[t * ldo + j] = (g * seq_sigmoid(alpha * g)) * (u + 1.0f);
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
 
 extern "C" {
 
-int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32_t vocab, int32_t d, int32_t streams, float* out, int32_t T,
-                   sllm_stream_t stream) {
+int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32_t vocab, int32_t d, int32_t streams, float scale, float* out,
+                   int32_t T, sllm_stream_t stream) {
     SLLM_REQUIRE(ids && table && out && T > 0 && d > 0 && vocab > 0 && streams >= 1, SLLM_EINVAL, "seq_embed: bad argument");
     SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_embed: fp32 or bf16 tables");
-    seq_embed_kernel<<<T, 128, 0, as_stream(stream)>>>(ids, table, w_dtype, vocab, d, streams, out, T);
+    seq_embed_kernel<<<T, 128, 0, as_stream(stream)>>>(ids, table, w_dtype, vocab, d, streams, scale, out, T);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
@@ -224,6 +284,36 @@ int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t 
     SLLM_REQUIRE(o && g && w && out && heads > 0 && dv > 0 && T > 0, SLLM_EINVAL, "seq_headnorm_gate: bad argument");
     const int items = T * heads;
     seq_headnorm_gate_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, T);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, int32_t T, int32_t d,
+                       sllm_stream_t stream) {
+    SLLM_REQUIRE(x && w && y && T > 0 && d > 0 && ldx >= d && ldy >= d, SLLM_EINVAL, "seq_layernorm: bad argument");
+    seq_layernorm_kernel<<<T, d >= 2048 ? 256 : 128, 0, as_stream(stream)>>>(x, ldx, w, bias, eps, y, ldy, d);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev, const float* coef, const float* norm_w, const float* norm_b, float eps,
+                           float* h, int32_t T, int32_t d, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && y && hist && coef && T > 0 && d > 0 && n_prev >= 0 && (!norm_w || h), SLLM_EINVAL, "seq_depth_average: bad argument");
+    SLLM_REQUIRE(n_prev <= kMaxDepth, SLLM_ENOTSUP, "seq_depth_average: %d earlier results beyond %d", n_prev, kMaxDepth);
+    seq_depth_average_kernel<<<T, d >= 2048 ? 256 : 128, 0, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_clamped_glu(const float* gate, int32_t ldg, const float* up, int32_t ldu, float limit, float alpha, float* out, int32_t ldo, int32_t T,
+                         int32_t n, sllm_stream_t stream) {
+    SLLM_REQUIRE(gate && up && out && T > 0 && n > 0 && ldg >= n && ldu >= n && ldo >= n, SLLM_EINVAL, "seq_clamped_glu: bad argument");
+    const size_t total = (size_t)T * n;
+    seq_clamped_glu_kernel<<<(int)std::min<size_t>((total + 255) / 256, (size_t)sm_count() * 8), 256, 0, as_stream(stream)>>>(gate, ldg, up, ldu, limit, alpha, out,
+                                                                                                                       ldo, T, n);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -1,7 +1,8 @@
 """Sequence-mixing and feed-forward mechanisms over the ragged-token-batch kernels (seqops.Ops), each with its constants as parameters so
 that a model description can combine them: fused input projections, softmax attention with (scaled, partial) rotary positions, rotated
-values and a head gate over a paged cache; a Griffin-style recurrent block (short causal convolution + real-gated linear recurrent unit);
-gated linear attention with a decay per key channel; a PolyNorm feed-forward. A mechanism says which per-sequence state it needs
+values and a head gate over a paged cache; softmax attention with unit-rms heads, capped scores, distance slopes and a window that keeps
+the first positions; latent attention (one cached row per token, absorbed form) with a sink and a head gate; a Griffin-style recurrent block (short causal convolution + real-gated linear recurrent unit);
+gated linear attention with a decay per key channel; a PolyNorm feed-forward; a clamped gated feed-forward. A mechanism says which per-sequence state it needs
 (``state_spec``); the engine's state manager owns that memory and hands it to ``forward`` — no mechanism keeps a cache of its own.
 
 Additive to the reference, whose only model is the Llama forward of source/model/model.cpp:40-140."""
@@ -84,6 +85,82 @@ class GatedRotaryAttention:
         ws = step.scratch("attn_ws", step.T * c.heads * step.nsplit * (c.vdim + 2))
         ops.attention(step.b, q, ld, c.heads, c.kv_heads, c.dim, c.vdim, c.scale, state["k"], state["v"], step.nsplit, ws, step.st)
         ops.attention_finish(step.b, ws, step.nsplit, c.heads, c.vdim, self.vfreq, self.layout, g, ld, out, self.width, step.st)
+
+
+def distance_slopes(heads: int, span: float = 8.0):
+    """Charge per position of distance for each head: head h of H gets 2^(-span (h+1) / H) (a geometric ladder down to 2^-span)."""
+    return [2.0 ** (-span * (h + 1) / heads) for h in range(heads)]
+
+
+class CappedWindowAttention:
+    """Softmax attention without rotation over a paged cache: every query, key and value head divided by its root mean square (no weight),
+    score = cap * tanh(q.k * scale / cap) - slope_h * distance, a sliding window that keeps the first positions of the sequence visible
+    at their true distance, grouped query heads. ``share`` = "keep": the values (after the division) are kept for later layers of the
+    step; "blend": v <- (1 - lambda) v + lambda * (the kept values of the same token), lambda = the tensor ``vmix``; the blended values
+    are what the cache holds."""
+
+    slope_span = 8.0
+
+    def __init__(self, cfg, w, pre, ops, device, eps, share=None):
+        self.cfg, self.ops, self.eps, self.share = cfg, ops, eps, share
+        self.inputs = [(w[pre + "q"], w.get(pre + "q.b")), (w[pre + "k"], w.get(pre + "k.b")), (w[pre + "v"], w.get(pre + "v.b"))]
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.slopes = torch.tensor(distance_slopes(cfg.heads, self.slope_span), dtype=torch.float32, device=device)
+        self.lam = float(w[pre + "vmix"].float().item()) if share == "blend" else 0.0
+        self.opts = ops.attention_options(cfg.mask.size, cfg.mask.keep_first, cfg.softcap, self.slopes)
+        self.width = cfg.heads * cfg.vdim
+
+    def state_spec(self):
+        return {"pages": [("k", self.cfg.kv_heads, self.cfg.dim), ("v", self.cfg.kv_heads, self.cfg.vdim)], "slots": []}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops = self.cfg, self.ops
+        q, k, v = cols
+        kept = step.scratch("v_kept", step.T * c.kv_heads * c.vdim) if self.share else None
+        ops.unit_kv(step.b, q, ld, c.heads, c.dim, k, ld, c.kv_heads, v, ld, c.vdim, self.eps, 7, kept, {None: 0, "keep": 1, "blend": 2}[self.share],
+                    self.lam, state["k"], state["v"], step.st)
+        ws = step.scratch("attn_ws", step.T * c.heads * step.nsplit * (c.vdim + 2))
+        ops.attention(step.b, q, ld, c.heads, c.kv_heads, c.dim, c.vdim, c.scale, state["k"], state["v"], step.nsplit, ws, step.st, opts=self.opts)
+        ops.attention_finish(step.b, ws, step.nsplit, c.heads, c.vdim, None, 0, None, 0, out, self.width, step.st)
+
+
+class LatentAttention:
+    """Attention over ONE cached row per token: c = RMS norm (weight) of the first kv_rank outputs of the down projection, and the last
+    rot_dim outputs rotated by the position, a key part all heads share. Head h's key is (W_uk,h c, rotated part), its value W_uv,h c.
+    Computed in the absorbed form, so that nothing but the cached row is read per key: the query of head h becomes (W_uk,h^T q_h, rotated
+    q part) against the row itself (one key/value head of width kv_rank + rot_dim whose first kv_rank columns are also the value), and W_uv,h
+    is applied to the head's weighted sum of rows. The softmax's denominator holds exp(sink_h); head h's output is multiplied by
+    sigmoid(g_h); then the output projection."""
+
+    def __init__(self, cfg, w, pre, ops, device, eps):
+        self.cfg, self.ops, self.eps = cfg, ops, eps
+        H, dn, dr, R = cfg.heads, cfg.dim, cfg.rot_dim, cfg.kv_rank
+        self.inputs = [(w[pre + "q"], w.get(pre + "q.b")), (w[pre + "dkv"], w.get(pre + "dkv.b")), (w[pre + "g"], w.get(pre + "g.b"))]
+        self.norm_w = w[pre + "dkv.norm"].float().contiguous()
+        self.uk_t = w[pre + "uk"].view(H, dn, R).transpose(1, 2).contiguous()       # [H][R][dn]: rows of W_uk,h^T
+        self.uv = w[pre + "uv"].contiguous()                                         # [H * vdim][R]
+        self.sink = w[pre + "sink"].float().contiguous() if pre + "sink" in w else None
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.freq = torch.tensor([cfg.rot.base ** (-2.0 * i / cfg.rot.dims) for i in range(cfg.rot.dims // 2)], dtype=torch.float64, device=device)
+        self.opts = ops.attention_options(cfg.mask.size, cfg.mask.keep_first, values_in_keys=True)
+        self.width = H * cfg.vdim
+
+    def state_spec(self):
+        return {"pages": [("row", 1, self.cfg.kv_rank + self.cfg.rot_dim)], "slots": []}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T = self.cfg, self.ops, step.T
+        H, dn, dr, R, dv = c.heads, c.dim, c.rot_dim, c.kv_rank, c.vdim
+        q, low, g = cols
+        wide = R + dr
+        qa = step.scratch("latent_q", T * H * wide)
+        ops.latent_kv(step.b, q, ld, H, dn, dr, low, ld, R, self.norm_w, self.eps, self.freq, c.rot.dims // 2, qa, H * wide, state["row"], step.st)
+        ops.linear(q, ld, self.uk_t, dn, None, qa.data_ptr(), H * wide, T, R, dn, step.st, batch=H, a_bs=dn + dr, w_bs=R * dn, c_bs=wide)
+        ws = step.scratch("attn_ws", T * H * step.nsplit * (R + 2))
+        ops.attention(step.b, qa.data_ptr(), H * wide, H, 1, wide, R, c.scale, state["row"], None, step.nsplit, ws, step.st, opts=self.opts)
+        mixed = step.scratch("latent_o", T * H * R)
+        ops.attention_finish(step.b, ws, step.nsplit, H, R, None, 0, g, ld, mixed, H * R, step.st, sink=self.sink)
+        ops.linear(mixed.data_ptr(), H * R, self.uv, R, None, out.data_ptr(), self.width, T, dv, R, step.st, batch=H, a_bs=R, w_bs=dv * R, c_bs=dv)
 
 
 class GatedLinearRecurrence:
@@ -190,6 +267,27 @@ class MixerGroup:
             sub = {k[len(name) + 1:]: t for k, t in state.items() if k.startswith(name + ".")}
             m.forward(step, [cols.data_ptr() + o * F32B for o in span], N, sub, part)
             m.out(step, part.data_ptr(), m.width, y.data_ptr(), m.out.N, alpha=weight, accumulate=i > 0)
+
+
+class ClampedGluFeedForward:
+    """Gated feed-forward with clamped branches: g = min(W_gate h + b, limit), u = clamp(W_up h + b, -limit, limit),
+    W_down (g * sigmoid(alpha g) * (u + 1)) + b. It has the interface of a mixer (``inputs`` / ``forward`` / ``out``), so that a
+    ``MixerGroup`` runs it beside a mixer on the same normed input: one fused input product, results added."""
+
+    alpha = 1.702
+
+    def __init__(self, cfg, w, pre, ops, device):
+        self.cfg, self.ops = cfg, ops
+        self.inputs = [(w[pre + "gate"], w.get(pre + "gate.b")), (w[pre + "up"], w.get(pre + "up.b"))]
+        self.out = FusedLinear([(w[pre + "down"], w.get(pre + "down.b"))], ops, device)
+        self.width = cfg.ff
+
+    def state_spec(self):
+        return {"pages": [], "slots": []}
+
+    def forward(self, step, cols, ld, state, out):
+        gate, up = cols
+        self.ops.clamped_glu(gate, ld, up, ld, self.cfg.limit, self.alpha, out, self.width, step.T, self.width, step.st)
 
 
 class PolyNormFeedForward:

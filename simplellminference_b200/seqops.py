@@ -36,8 +36,17 @@ class Ops:
             raise _lib.SllmError(rc, self.lib.sllm_last_error().decode(errors="replace"))
 
     # ---- rows ----
-    def embed(self, ids, table, vocab, d, streams, out, T, st):
-        self._ck(self.lib.sllm_seq_embed(_p(ids), _p(table), self.w_dtype, vocab, d, streams, _p(out), T, st))
+    def embed(self, ids, table, vocab, d, streams, out, T, st, scale=1.0):
+        self._ck(self.lib.sllm_seq_embed(_p(ids), _p(table), self.w_dtype, vocab, d, streams, scale, _p(out), T, st))
+
+    def layernorm(self, x, ldx, w, bias, eps, y, ldy, T, d, st):
+        self._ck(self.lib.sllm_seq_layernorm(_p(x), ldx, _p(w), _p(bias), eps, _p(y), ldy, T, d, st))
+
+    def depth_average(self, x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d, st):
+        self._ck(self.lib.sllm_seq_depth_average(_p(x), _p(y), _p(hist), n_prev, _p(coef), _p(norm_w), _p(norm_b), eps, _p(h), T, d, st))
+
+    def clamped_glu(self, gate_ptr, ldg, up_ptr, ldu, limit, alpha, out, ldo, T, n, st):
+        self._ck(self.lib.sllm_seq_clamped_glu(gate_ptr, ldg, up_ptr, ldu, limit, alpha, _p(out), ldo, T, n, st))
 
     def hyper_read(self, x, streams, T, d, coef, norm_w, groups, eps, y, st):
         self._ck(self.lib.sllm_seq_hyper_read(_p(x), streams, T, d, _p(coef), _p(norm_w), groups, eps, _p(y), st))
@@ -67,12 +76,25 @@ class Ops:
         self._ck(self.lib.sllm_seq_rotary_kv(C.byref(b), q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, _p(freq), n_freq, magnitude,
                                              _p(vfreq), layout, _p(k_pool), _p(v_pool), self.kv_dtype, st))
 
-    def attention(self, b, q_ptr, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, st):
+    def attention(self, b, q_ptr, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, st, opts=None):
         self._ck(self.lib.sllm_seq_attention(C.byref(b), q_ptr, ldq, heads, kv_heads, dk, dv, scale, _p(k_pool), _p(v_pool), self.kv_dtype, nsplit,
-                                             _p(ws), st))
+                                             _p(ws), C.byref(opts) if opts is not None else None, st))
 
-    def attention_finish(self, b, ws, nsplit, heads, dv, vfreq, layout, gate_ptr, ldg, out, ldo, st):
-        self._ck(self.lib.sllm_seq_attention_finish(C.byref(b), _p(ws), nsplit, heads, dv, _p(vfreq), layout, gate_ptr, ldg, _p(out), ldo, st))
+    def attention_finish(self, b, ws, nsplit, heads, dv, vfreq, layout, gate_ptr, ldg, out, ldo, st, sink=None):
+        self._ck(self.lib.sllm_seq_attention_finish(C.byref(b), _p(ws), nsplit, heads, dv, _p(vfreq), layout, gate_ptr, ldg, _p(sink), _p(out), ldo, st))
+
+    @staticmethod
+    def attention_options(window=0, keep_first=0, softcap=0.0, slopes=None, values_in_keys=False):
+        """The options structure of ``attention``; the caller keeps the ``slopes`` tensor alive."""
+        return _lib.SeqAttnOpts(int(window or 0), int(keep_first or 0), float(softcap or 0.0), _p(slopes), int(bool(values_in_keys)))
+
+    def unit_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, eps, unit, v_shared, share, lam, k_pool, v_pool, st):
+        self._ck(self.lib.sllm_seq_unit_kv(C.byref(b), q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, eps, unit, _p(v_shared), share, lam,
+                                           _p(k_pool), _p(v_pool), self.kv_dtype, st))
+
+    def latent_kv(self, b, q_ptr, ldq, heads, dn, dr, low_ptr, ldlow, rank, norm_w, eps, freq, n_freq, q_out, ldqo, pool, st):
+        self._ck(self.lib.sllm_seq_latent_kv(C.byref(b), q_ptr, ldq, heads, dn, dr, low_ptr, ldlow, rank, _p(norm_w), eps, _p(freq), n_freq, _p(q_out),
+                                             ldqo, _p(pool), self.kv_dtype, st))
 
     # ---- recurrences ----
     def conv(self, b, x_ptr, ldx, channels, taps, w, cb, tail, u, ldu, st):
