@@ -65,6 +65,10 @@ def parse():
                     help="instead of the headline workload: prefill and decode throughput of the Munazen design (softmax attention + recurrent mixers over the "
                          "ragged-batch engine) at real layer sizes beside the Llama engine at equal size; comma-separated sizes of "
                          "simplellminference_b200/bench_hybrid.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"hybrid\": [...]}")
+    ap.add_argument("--sopetar", default=None, metavar="SIZES",
+                    help="instead of the headline workload: prefill and decode throughput of the Sopetar design (windowed capped attention + latent attention, "
+                         "parallel layers, depth-weighted average) beside the Llama engine at equal size; comma-separated sizes of "
+                         "simplellminference_b200/bench_sopetar.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"sopetar\": [...]}")
     ap.add_argument("--no-batch", action="store_true", help="(kept for old command lines: the secondary measurements are opt-in now, see --extras)")
     return ap.parse_args()
 
@@ -640,18 +644,23 @@ def main():
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
-    if args.hybrid:
+    if args.hybrid or args.sopetar:
         import torch
-        from simplellminference_b200 import bench_hybrid
+        if args.hybrid:
+            from simplellminference_b200 import bench_hybrid
+            key, wanted = "hybrid", args.hybrid
+        else:
+            from simplellminference_b200 import bench_sopetar as bench_hybrid
+            key, wanted = "sopetar", args.sopetar
         torch.cuda.set_device(0)
-        sizes = list(bench_hybrid.SIZES) if args.hybrid == "all" else args.hybrid.split(",")
+        sizes = list(bench_hybrid.SIZES) if wanted == "all" else wanted.split(",")
         hbm, hbm_src = peaks()
         tf, tf_src = tensor_peak()
         real = sys.stdout
         sys.stdout = sys.stderr                      # the per-size lines are progress; stdout carries exactly ONE line
         res = bench_hybrid.main(sizes, hbm, tf)
         sys.stdout = real
-        print(json.dumps({"hybrid": res, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf, "bf16_source": tf_src}}))
+        print(json.dumps({key: res, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf, "bf16_source": tf_src}}))
         return
     if args.impl == "reference":
         run_reference(args)

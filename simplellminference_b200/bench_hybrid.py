@@ -170,14 +170,14 @@ def bench_munazen(name: str, hbm_gbs: float, tflops: float) -> dict:
     return out
 
 
-def bench_llama(name: str, hbm_gbs: float, tflops: float) -> dict:
+def bench_llama(name: str, hbm_gbs: float, tflops: float, size: dict | None = None) -> dict:
     """The closest model of the framework at the same width, depth and head geometry: its batched tensor-core prefill and its
     one-sequence decode step (device-resident greedy loop)."""
     import torch
 
     from .config import BF16, ModelShape
     from .engine import Engine
-    size = SIZES[name]
+    size = size or SIZES[name]
     d, layers, T = size["width"], 4 * size["repeats"], size["prompt"]
     heads = d // 128
     inter = ((8 * d // 3) + 255) // 256 * 256

@@ -36,6 +36,7 @@ struct PfGemmArgs {
     uint16_t* s_out;      // bf16 [T][I_loc]
     int32_t I_loc;
     int32_t bn;           // 0 = choose; 128 / 256 = force the N tile
+    const float* bias;    // STORE / RESID / ACCUM: fp32 [N] added to every row of C (once, whatever the split of K), or NULL
 };
 
 struct PfCache;   // tensor-map cache (one CUtensorMap per weight matrix and tile shape), owned by the engine

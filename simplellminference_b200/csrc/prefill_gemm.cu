@@ -55,6 +55,7 @@ struct PfDev {           // kernel-side view of PfGemmArgs
     uint16_t* q_out; uint8_t *kc, *vc; int32_t kv_dtype, q_loc, kv_loc, hd, S, pos0;
     const float *sin_t, *cos_t;
     uint16_t* s_out; int32_t I_loc;
+    const float* bias;
 };
 
 // ------------------------------------------------------------------------------------------ PTX -------
@@ -425,6 +426,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                 tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + c0), v);
                 const int n0 = n_tile * BN + c0;
                 if (t < p.T && n0 < p.N) {
+                    if (p.bias && unit % p.ksplit == 0) {   // the bias rides on the first share of K
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + i < p.n_valid) v[i] = __float_as_uint(__uint_as_float(v[i]) + p.bias[n0 + i]);
+                    }
                     if (p.epilogue == PF_EPI_QKV) epi_qkv(p, t, n0, v);
                     else if (p.epilogue == PF_EPI_GATEUP) epi_gateup(p, t, n0, v);
                     else if (p.ksplit > 1) epi_red_add(p, t, n0, v);
@@ -574,6 +580,7 @@ int pf_gemm(PfCache* cache, const PfGemmArgs& a, cudaStream_t st) {
     p.out = a.out; p.ld_out = a.ld_out; p.n_valid = a.n_valid;
     p.q_out = a.q_out; p.kc = a.k_cache; p.vc = a.v_cache; p.kv_dtype = a.kv_dtype; p.q_loc = a.q_loc; p.kv_loc = a.kv_loc; p.hd = a.hd; p.S = a.S;
     p.pos0 = a.pos0; p.sin_t = a.sin_t; p.cos_t = a.cos_t; p.s_out = a.s_out; p.I_loc = a.I_loc;
+    p.bias = (a.epilogue == PF_EPI_STORE || a.epilogue == PF_EPI_RESID || a.epilogue == PF_EPI_ACCUM) ? a.bias : nullptr;
 
     CUtensorMap tmA;
     {

@@ -178,25 +178,59 @@ __global__ void seq_layernorm_kernel(const float* __restrict__ x, int ldx, const
 constexpr int kMaxDepth = 256;
 
 // One CTA per token: hist[n_prev] <- x + y (this layer's own result); x <- sum_{j <= n_prev} coef[j] * hist[j]; h <- layer norm of x.
-// A thread re-reads only what it wrote itself until the norm, whose reductions order the rest.
-__global__ void seq_depth_average_kernel(float* __restrict__ x, const float* __restrict__ y, float* __restrict__ hist, int n_prev, const float* __restrict__ coef,
+// The new row stays in shared memory for the norm's passes; with rows of a multiple of four floats everything moves as 16-byte words and
+// the loads of the earlier results are issued together, before the store into the same array.
+template <typename V>
+__global__ void seq_depth_average_kernel(float* __restrict__ x, const float* __restrict__ y, float* hist, int n_prev, const float* __restrict__ coef,
                                          const float* __restrict__ norm_w, const float* __restrict__ norm_b, float eps, float* __restrict__ h, int T, int d) {
+    extern __shared__ __align__(16) float s_row[];   // [d]
     __shared__ float red[33];
     __shared__ float s_coef[kMaxDepth + 1];
+    constexpr int E = sizeof(V) / sizeof(float);
     const int t = blockIdx.x;
     for (int j = threadIdx.x; j <= n_prev; j += blockDim.x) s_coef[j] = coef[j];
     __syncthreads();
-    const size_t plane = (size_t)T * d, row = (size_t)t * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        const float own = x[row + j] + y[row + j];
-        hist[(size_t)n_prev * plane + row + j] = own;
-        float u = 0.0f;
-        for (int l = 0; l < n_prev; ++l) u = fmaf(s_coef[l], hist[(size_t)l * plane + row + j], u);
-        x[row + j] = fmaf(s_coef[n_prev], own, u);
+    const size_t plane = (size_t)T * d / E, row = (size_t)t * d / E;
+    V* xv = reinterpret_cast<V*>(x) + row;
+    const V* yv = reinterpret_cast<const V*>(y) + row;
+    V* hv = reinterpret_cast<V*>(hist) + row;
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < d / E; c += blockDim.x) {
+        V own = xv[c];
+        const V add = yv[c];
+        float u[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            reinterpret_cast<float*>(&own)[e] += reinterpret_cast<const float*>(&add)[e];
+            u[e] = 0.0f;
+        }
+#pragma unroll 4
+        for (int l = 0; l < n_prev; ++l) {
+            const V old = hv[(size_t)l * plane + c];
+#pragma unroll
+            for (int e = 0; e < E; ++e) u[e] = fmaf(s_coef[l], reinterpret_cast<const float*>(&old)[e], u[e]);
+        }
+        hv[(size_t)n_prev * plane + c] = own;
+        V out;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float v = fmaf(s_coef[n_prev], reinterpret_cast<const float*>(&own)[e], u[e]);
+            reinterpret_cast<float*>(&out)[e] = v;
+            s_row[c * E + e] = v;
+            sum += v;
+        }
+        xv[c] = out;
     }
     if (!norm_w) return;
-    __syncthreads();
-    seq_layernorm_row(x + row, norm_w, norm_b, eps, h + row, d, red);
+    const float mean = block_sum(sum, red) / (float)d;   // its barriers also publish s_row
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float c = s_row[j] - mean;
+        ss = fmaf(c, c, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+    float* hr = h + (size_t)t * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) hr[j] = ((s_row[j] - mean) * inv) * norm_w[j] + (norm_b ? norm_b[j] : 0.0f);
 }
 
 // out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
@@ -302,7 +336,17 @@ int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev
                            float* h, int32_t T, int32_t d, sllm_stream_t stream) {
     SLLM_REQUIRE(x && y && hist && coef && T > 0 && d > 0 && n_prev >= 0 && (!norm_w || h), SLLM_EINVAL, "seq_depth_average: bad argument");
     SLLM_REQUIRE(n_prev <= kMaxDepth, SLLM_ENOTSUP, "seq_depth_average: %d earlier results beyond %d", n_prev, kMaxDepth);
-    seq_depth_average_kernel<<<T, d >= 2048 ? 256 : 128, 0, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d);
+    const size_t smem = (size_t)d * sizeof(float);
+    SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 4096, SLLM_ENOTSUP, "seq_depth_average: rows of %d floats do not fit shared memory", d);
+    const bool vec = d % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)hist % 16) == 0;
+    const int threads = d >= 2048 ? 256 : 128;
+    if (vec) {
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_depth_average_kernel<float4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        seq_depth_average_kernel<float4><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d);
+    } else {
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_depth_average_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        seq_depth_average_kernel<float><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d);
+    }
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

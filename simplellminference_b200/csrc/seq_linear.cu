@@ -5,7 +5,7 @@
 //   * tile_kernel  (any shape): 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMAs with fp32 accumulation. This is
 //     the body of the all-fp32 mode, and of bf16 products whose shape the tensor-core tiles do not take;
 //   * the tcgen05 GEMM of the prefill path (prefill_gemm.cu) for bf16 weights when the caller passes a bf16 scratch for A and the shape
-//     fits its TMA boxes; without bias and scale the GEMM's own epilogue stores (or adds) into C, otherwise bias, alpha and accumulation
+//     fits its TMA boxes; without a scale the GEMM's own epilogue adds the bias and stores (or adds) into C, otherwise bias, alpha and accumulation
 //     run as a short epilogue kernel over C.
 // In bf16 mode (round_a) the activations are rounded to bf16 as they are loaded, so all three bodies multiply the same operands and
 // differ only in summation order.
@@ -225,8 +225,9 @@ extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32
         SLLM_LAUNCH_CHECK();
         PfGemmArgs a{};
         a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.bn = 0; a.n_valid = N;
-        if (!bias && alpha == 1.0f && ((uintptr_t)C % 16) == 0) {
-            // nothing to do after the product: the GEMM's own epilogue stores (or adds) straight into C
+        if (alpha == 1.0f && ((uintptr_t)C % 16) == 0) {
+            // nothing but the bias to do after the product: the GEMM's own epilogue adds it and stores (or adds) straight into C
+            a.bias = bias;
             a.epilogue = accumulate ? PF_EPI_RESID : PF_EPI_STORE; a.out = C; a.ld_out = ldc;
             return pf_gemm(cache, a, st);
         }
