@@ -430,10 +430,14 @@ int sllm_seq_hyper_write_read(float* x, int32_t streams, int32_t T, int32_t d, c
 /* C[b] = alpha * (A[b] . W[b]^T + bias[b]) (+ C[b] if accumulate): A fp32 [T][lda] (rounded to bf16 on load if round_a), W [N][ldw]
  * row-major in w_dtype, bias fp32 [N] or NULL, C fp32 [T][ldc]; `batch` independent products whose operands lie *_bs elements apart
  * (block-diagonal matrices). Any T, N, K. With a16 (scratch of T*K bf16 values) given, bf16 weights and a shape its tiles take, the
- * product runs on the tensor cores (tcgen05); otherwise on fp32 FMAs. */
+ * product runs on the tensor cores (tcgen05); otherwise on fp32 FMAs. a16_ready != 0: the kernel that produced A has already left
+ * its rows in a16 as dense bf16 [T][K] (sllm_seq_depth_average, sllm_seq_layernorm and sllm_seq_clamped_glu can), so that the copy is
+ * skipped; only meaningful when sllm_seq_linear_on_tensor_cores says the product goes there. */
 int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc,
                     int32_t T, int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs,
-                    int64_t w_bs, int64_t bias_bs, int64_t c_bs, void* a16, sllm_stream_t stream);
+                    int64_t w_bs, int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, sllm_stream_t stream);
+/* 1 when sllm_seq_linear with a bf16 scratch sends this shape to the tensor cores (the weights must also be 16-byte aligned) */
+int sllm_seq_linear_on_tensor_cores(int32_t T, int32_t N, int32_t K, int32_t w_dtype, int32_t ldw, int32_t batch, int32_t round_a);
 /* PolyNorm: out = c0*N(z) + c1*N(z^2) + c2*N(z^3) + c3, powers element-wise, N(v) = v / sqrt(mean(v^2) + eps) over a row; coef: 4 floats */
 int sllm_seq_polynorm(const float* z, int32_t ldz, const float* coef, float eps, float* out, int32_t ldo, int32_t T, int32_t n,
                       sllm_stream_t stream);
@@ -482,17 +486,19 @@ int sllm_seq_unit_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t hea
 int sllm_seq_latent_kv(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t dn, int32_t dr, const float* low,
                        int32_t ldlow, int32_t rank, const float* norm_w, float eps, const double* freq, int32_t n_freq, float* q_out,
                        int32_t ldqo, void* pool, int32_t kv_dtype, sllm_stream_t stream);
-/* y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + bias per row (bias NULL = none) */
-int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, int32_t T,
-                       int32_t d, sllm_stream_t stream);
+/* y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + bias per row (bias NULL = none); y16 (or NULL): the same rows once more, rounded
+ * to bf16, dense [T][d] — the operand copy of a tensor-core product that follows */
+int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, void* y16,
+                       int32_t T, int32_t d, sllm_stream_t stream);
 /* Depth-weighted average: hist [n_prev + 1 ..][T][d] holds the embedding output and every earlier layer's own result. Stores this
  * layer's result hist[n_prev] = x + y, replaces x by sum_{j <= n_prev} coef[j] * hist[j], and, with norm_w, writes the layer norm
- * (norm_w, norm_b, eps) of the new x to h. */
+ * (norm_w, norm_b, eps) of the new x to h, and to h16 (if given) as dense bf16 rows. */
 int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev, const float* coef, const float* norm_w,
-                           const float* norm_b, float eps, float* h, int32_t T, int32_t d, sllm_stream_t stream);
-/* out = g * sigmoid(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), element-wise over [T][n] */
+                           const float* norm_b, float eps, float* h, void* h16, int32_t T, int32_t d, sllm_stream_t stream);
+/* out = g * sigmoid(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), element-wise over [T][n]; out16 (or NULL):
+ * the result also as dense bf16 [T][n] (then out may be NULL) */
 int sllm_seq_clamped_glu(const float* gate, int32_t ldg, const float* up, int32_t ldu, float limit, float alpha, float* out, int32_t ldo,
-                         int32_t T, int32_t n, sllm_stream_t stream);
+                         void* out16, int32_t T, int32_t n, sllm_stream_t stream);
 /* Causal convolution per channel over each sequence: u[t][c] = cb[c] + sum_k w[c][k] * x[t - (taps-1-k)][c]; inputs before the segment
  * come from tail[slot][taps-1][channels] (zeros for a new sequence). The tail is NOT updated here (sllm_seq_rglru_scan does it). */
 int sllm_seq_conv(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* cb,

@@ -134,7 +134,8 @@ SIGNATURES.update({
     "sllm_seq_hyper_read": (C.c_int, [_P, _I, _I, _I, _P, _P, _I, _F, _P, _P]),
     "sllm_seq_hyper_write": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "sllm_seq_hyper_write_read": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _F, _P, _P]),
-    "sllm_seq_linear": (C.c_int, [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _L, _L, _L, _L, _P, _P]),
+    "sllm_seq_linear": (C.c_int, [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _L, _L, _L, _L, _P, _I, _P]),
+    "sllm_seq_linear_on_tensor_cores": (C.c_int, [_I, _I, _I, _I, _I, _I, _I]),
     "sllm_seq_polynorm": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "sllm_seq_gather_rows": (C.c_int, [_P, _I, _P, _I, _I, _P, _P]),
     "sllm_seq_rotary_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _F, _P, _I, _P, _P, _I, _P]),
@@ -142,9 +143,9 @@ SIGNATURES.update({
     "sllm_seq_attention_finish": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _P]),
     "sllm_seq_unit_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _F, _P, _P, _I, _P]),
     "sllm_seq_latent_kv": (C.c_int, [_B, _P, _I, _I, _I, _I, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P]),
-    "sllm_seq_layernorm": (C.c_int, [_P, _I, _P, _P, _F, _P, _I, _I, _I, _P]),
-    "sllm_seq_depth_average": (C.c_int, [_P, _P, _P, _I, _P, _P, _P, _F, _P, _I, _I, _P]),
-    "sllm_seq_clamped_glu": (C.c_int, [_P, _I, _P, _I, _F, _F, _P, _I, _I, _I, _P]),
+    "sllm_seq_layernorm": (C.c_int, [_P, _I, _P, _P, _F, _P, _I, _P, _I, _I, _P]),
+    "sllm_seq_depth_average": (C.c_int, [_P, _P, _P, _I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
+    "sllm_seq_clamped_glu": (C.c_int, [_P, _I, _P, _I, _F, _F, _P, _I, _P, _I, _I, _P]),
     "sllm_seq_conv": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "sllm_seq_rglru_scan": (C.c_int, [_B, _P, _I, _P, _P, _I, _P, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _I, _P, _P]),
     "sllm_seq_gla_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _P]),

@@ -156,7 +156,7 @@ __global__ void seq_headnorm_gate_kernel(const float* __restrict__ o, int ldo, c
 // (row - mean) / sqrt(variance + eps) * w + b of one row that the CTA's threads hold strided; the variance is the mean of the squared
 // deviations (two passes: the mean first), as the definition says
 __device__ __forceinline__ void seq_layernorm_row(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, float eps,
-                                                  float* __restrict__ y, int d, float* red) {
+                                                  float* __restrict__ y, uint16_t* __restrict__ y16, int d, float* red) {
     float s = 0.0f;
     for (int j = threadIdx.x; j < d; j += blockDim.x) s += x[j];
     const float mean = block_sum(s, red) / (float)d;
@@ -166,13 +166,17 @@ __device__ __forceinline__ void seq_layernorm_row(const float* __restrict__ x, c
         ss = fmaf(c, c, ss);
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-    for (int j = threadIdx.x; j < d; j += blockDim.x) y[j] = ((x[j] - mean) * inv) * w[j] + (bias ? bias[j] : 0.0f);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = ((x[j] - mean) * inv) * w[j] + (bias ? bias[j] : 0.0f);
+        y[j] = v;
+        if (y16) y16[j] = f32_to_bf16_bits(v);
+    }
 }
 
 __global__ void seq_layernorm_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias, float eps,
-                                     float* __restrict__ y, int ldy, int d) {
+                                     float* __restrict__ y, int ldy, uint16_t* __restrict__ y16, int d) {
     __shared__ float red[33];
-    seq_layernorm_row(x + (size_t)blockIdx.x * ldx, w, bias, eps, y + (size_t)blockIdx.x * ldy, d, red);
+    seq_layernorm_row(x + (size_t)blockIdx.x * ldx, w, bias, eps, y + (size_t)blockIdx.x * ldy, y16 ? y16 + (size_t)blockIdx.x * d : nullptr, d, red);
 }
 
 constexpr int kMaxDepth = 256;
@@ -182,7 +186,7 @@ constexpr int kMaxDepth = 256;
 // the loads of the earlier results are issued together, before the store into the same array.
 template <typename V>
 __global__ void seq_depth_average_kernel(float* __restrict__ x, const float* __restrict__ y, float* hist, int n_prev, const float* __restrict__ coef,
-                                         const float* __restrict__ norm_w, const float* __restrict__ norm_b, float eps, float* __restrict__ h, int T, int d) {
+                                         const float* __restrict__ norm_w, const float* __restrict__ norm_b, float eps, float* __restrict__ h, uint16_t* __restrict__ h16, int T, int d) {
     extern __shared__ __align__(16) float s_row[];   // [d]
     __shared__ float red[33];
     __shared__ float s_coef[kMaxDepth + 1];
@@ -230,18 +234,24 @@ __global__ void seq_depth_average_kernel(float* __restrict__ x, const float* __r
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
     float* hr = h + (size_t)t * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) hr[j] = ((s_row[j] - mean) * inv) * norm_w[j] + (norm_b ? norm_b[j] : 0.0f);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = ((s_row[j] - mean) * inv) * norm_w[j] + (norm_b ? norm_b[j] : 0.0f);
+        hr[j] = v;
+        if (h16) h16[(size_t)t * d + j] = f32_to_bf16_bits(v);
+    }
 }
 
 // out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
 __global__ void seq_clamped_glu_kernel(const float* __restrict__ gate, int ldg, const float* __restrict__ up, int ldu, float limit, float alpha,
-                                       float* __restrict__ out, int ldo, int T, int n) {
+                                       float* __restrict__ out, int ldo, uint16_t* __restrict__ out16, int T, int n) {
     const size_t total = (size_t)T * n;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / n, j = i % n;
         const float g = fminf(gate[t * ldg + j], limit);
         const float u = fminf(fmaxf(up[t * ldu + j], -limit), limit);
-        out[t * ldo + j] = (g * seq_sigmoid(alpha * g)) * (u + 1.0f);
+        const float v = (g * seq_sigmoid(alpha * g)) * (u + 1.0f);
+        if (out) out[t * ldo + j] = v;
+        if (out16) out16[i] = f32_to_bf16_bits(v);
     }
 }
 
@@ -323,17 +333,17 @@ int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t 
     return SLLM_OK;
 }
 
-int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, int32_t T, int32_t d,
-                       sllm_stream_t stream) {
+int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, void* y16, int32_t T,
+                       int32_t d, sllm_stream_t stream) {
     SLLM_REQUIRE(x && w && y && T > 0 && d > 0 && ldx >= d && ldy >= d, SLLM_EINVAL, "seq_layernorm: bad argument");
-    seq_layernorm_kernel<<<T, d >= 2048 ? 256 : 128, 0, as_stream(stream)>>>(x, ldx, w, bias, eps, y, ldy, d);
+    seq_layernorm_kernel<<<T, d >= 2048 ? 256 : 128, 0, as_stream(stream)>>>(x, ldx, w, bias, eps, y, ldy, (uint16_t*)y16, d);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
 }
 
 int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev, const float* coef, const float* norm_w, const float* norm_b, float eps,
-                           float* h, int32_t T, int32_t d, sllm_stream_t stream) {
+                           float* h, void* h16, int32_t T, int32_t d, sllm_stream_t stream) {
     SLLM_REQUIRE(x && y && hist && coef && T > 0 && d > 0 && n_prev >= 0 && (!norm_w || h), SLLM_EINVAL, "seq_depth_average: bad argument");
     SLLM_REQUIRE(n_prev <= kMaxDepth, SLLM_ENOTSUP, "seq_depth_average: %d earlier results beyond %d", n_prev, kMaxDepth);
     const size_t smem = (size_t)d * sizeof(float);
@@ -342,22 +352,22 @@ int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev
     const int threads = d >= 2048 ? 256 : 128;
     if (vec) {
         if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_depth_average_kernel<float4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        seq_depth_average_kernel<float4><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d);
+        seq_depth_average_kernel<float4><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, (uint16_t*)h16, T, d);
     } else {
         if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_depth_average_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        seq_depth_average_kernel<float><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d);
+        seq_depth_average_kernel<float><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, (uint16_t*)h16, T, d);
     }
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
 }
 
-int sllm_seq_clamped_glu(const float* gate, int32_t ldg, const float* up, int32_t ldu, float limit, float alpha, float* out, int32_t ldo, int32_t T,
-                         int32_t n, sllm_stream_t stream) {
-    SLLM_REQUIRE(gate && up && out && T > 0 && n > 0 && ldg >= n && ldu >= n && ldo >= n, SLLM_EINVAL, "seq_clamped_glu: bad argument");
+int sllm_seq_clamped_glu(const float* gate, int32_t ldg, const float* up, int32_t ldu, float limit, float alpha, float* out, int32_t ldo, void* out16,
+                         int32_t T, int32_t n, sllm_stream_t stream) {
+    SLLM_REQUIRE(gate && up && (out || out16) && T > 0 && n > 0 && ldg >= n && ldu >= n && (!out || ldo >= n), SLLM_EINVAL, "seq_clamped_glu: bad argument");
     const size_t total = (size_t)T * n;
     seq_clamped_glu_kernel<<<(int)std::min<size_t>((total + 255) / 256, (size_t)sm_count() * 8), 256, 0, as_stream(stream)>>>(gate, ldg, up, ldu, limit, alpha, out,
-                                                                                                                       ldo, T, n);
+                                                                                                                       ldo, (uint16_t*)out16, T, n);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -194,9 +194,14 @@ __global__ void seq_linear_epilogue_kernel(const float* __restrict__ P, const fl
 
 using namespace sllm;
 
+extern "C" int sllm_seq_linear_on_tensor_cores(int32_t T, int32_t N, int32_t K, int32_t w_dtype, int32_t ldw, int32_t batch, int32_t round_a) {
+    // bf16 weights and operands, rows that TMA can address (16-byte multiples) and enough work to fill tiles
+    return w_dtype == SLLM_BF16 && batch == 1 && round_a && T >= 64 && N >= 64 && K >= 64 && K % 8 == 0 && ldw == K && N % 4 == 0;
+}
+
 extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc, int32_t T,
                                int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs, int64_t w_bs,
-                               int64_t bias_bs, int64_t c_bs, void* a16, sllm_stream_t stream) {
+                               int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, sllm_stream_t stream) {
     SLLM_REQUIRE(A && W && C && T > 0 && N > 0 && K > 0 && batch >= 1, SLLM_EINVAL, "seq_linear: bad argument");
     SLLM_REQUIRE(lda >= K && ldw >= K && ldc >= N, SLLM_EINVAL, "seq_linear: row strides shorter than the rows");
     SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_linear: fp32 or bf16 weights");
@@ -216,13 +221,14 @@ extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32
         return SLLM_OK;
     }
     // tensor cores: bf16 weights, a dense bf16 copy of A, rows that TMA can address (16-byte multiples) and enough work to fill tiles
-    if (a16 && w_dtype == SLLM_BF16 && batch == 1 && round_a && T >= 64 && N >= 64 && K >= 64 && K % 8 == 0 && ldw == K && N % 4 == 0 &&
-        ((uintptr_t)W % 16) == 0) {
+    if (a16 && sllm_seq_linear_on_tensor_cores(T, N, K, w_dtype, ldw, batch, round_a) && ((uintptr_t)W % 16) == 0) {
         static PfCache* cache = pf_cache_create();
-        const size_t n = (size_t)T * K;
-        seq_to_bf16_kernel<<<(int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8), 256, 0, st>>>(A, lda, reinterpret_cast<uint16_t*>(a16), T, K);
-        ++g_launches;
-        SLLM_LAUNCH_CHECK();
+        if (!a16_ready) {   // else the kernel that produced A has left its bf16 rows in a16 already
+            const size_t n = (size_t)T * K;
+            seq_to_bf16_kernel<<<(int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8), 256, 0, st>>>(A, lda, reinterpret_cast<uint16_t*>(a16), T, K);
+            ++g_launches;
+            SLLM_LAUNCH_CHECK();
+        }
         PfGemmArgs a{};
         a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.bn = 0; a.n_valid = N;
         if (alpha == 1.0f && ((uintptr_t)C % 16) == 0) {

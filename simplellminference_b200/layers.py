@@ -54,10 +54,18 @@ class FusedLinear:
         else:
             self.bias = None
 
-    def __call__(self, step, a_ptr, lda, c_ptr, ldc, alpha=1.0, accumulate=False):
+    def __call__(self, step, a_ptr, lda, c_ptr, ldc, alpha=1.0, accumulate=False, a16_ready=False):
         scratch = step.gemm_scratch(self.K, self.N)
         self.ops.linear(a_ptr, lda, self.w, self.K, self.bias, c_ptr, ldc, step.T, self.N, self.K, step.st, alpha=alpha, accumulate=accumulate,
-                        scratch=scratch)
+                        scratch=scratch, a16_ready=a16_ready and scratch is not None)
+
+    def operand_rows(self, step):
+        """Where a kernel that produces this product's input may leave it as bf16 rows [T][K] (then call with ``a16_ready``), or None when
+        the product does not run on the tensor cores in this step."""
+        scratch = step.gemm_scratch(self.K, self.N)
+        if scratch is None or not self.ops.on_tensor_cores(step.T, self.N, self.K) or self.w.data_ptr() % 16:
+            return None
+        return scratch
 
 
 class GatedRotaryAttention:
@@ -257,16 +265,17 @@ class MixerGroup:
             spec["slots"] += [(f"{name}.{n}", shape) for n, shape in s["slots"]]
         return spec
 
-    def forward(self, step, h, state, y):
-        """h [T][d] -> y [T][d]"""
+    def forward(self, step, h, state, y, h16_ready=False):
+        """h [T][d] -> y [T][d]; ``h16_ready``: the kernel that wrote h also left it in ``self.proj.operand_rows(step)``."""
         T, N = step.T, self.proj.N
         cols = step.scratch("mix_cols", T * N)
-        self.proj(step, h.data_ptr(), self.proj.K, cols.data_ptr(), N)
+        self.proj(step, h.data_ptr(), self.proj.K, cols.data_ptr(), N, a16_ready=h16_ready)
         for i, ((name, m, weight), span) in enumerate(zip(self.members, self.spans)):
             part = step.scratch("mix_part", T * m.width)
             sub = {k[len(name) + 1:]: t for k, t in state.items() if k.startswith(name + ".")}
-            m.forward(step, [cols.data_ptr() + o * F32B for o in span], N, sub, part)
-            m.out(step, part.data_ptr(), m.width, y.data_ptr(), m.out.N, alpha=weight, accumulate=i > 0)
+            # a member whose forward says True has left its result as bf16 operand rows of its output projection
+            ready = m.forward(step, [cols.data_ptr() + o * F32B for o in span], N, sub, part)
+            m.out(step, part.data_ptr(), m.width, y.data_ptr(), m.out.N, alpha=weight, accumulate=i > 0, a16_ready=ready is True)
 
 
 class ClampedGluFeedForward:
@@ -287,7 +296,10 @@ class ClampedGluFeedForward:
 
     def forward(self, step, cols, ld, state, out):
         gate, up = cols
-        self.ops.clamped_glu(gate, ld, up, ld, self.cfg.limit, self.alpha, out, self.width, step.T, self.width, step.st)
+        rows16 = self.out.operand_rows(step)       # the down projection on the tensor cores reads bf16 rows: write those, and only those
+        self.ops.clamped_glu(gate, ld, up, ld, self.cfg.limit, self.alpha, None if rows16 is not None else out, self.width, step.T, self.width, step.st,
+                             out16=rows16)
+        return rows16 is not None
 
 
 class PolyNormFeedForward:

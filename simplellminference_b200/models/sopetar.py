@@ -58,13 +58,16 @@ class SopetarModel:
         y = step.scratch("sub_out", T * d)
         ops.embed(ids, self.embed, self.vocab, d, 2, planes, T, step.st, scale=c.embedding_scale)   # layer 0 reads the embedding output itself
         first = self.layers[0]
-        ops.layernorm(x, d, first.norm_w, first.norm_b, c.norm_eps, h, d, T, d, step.st)
+        # a norm whose rows feed a tensor-core product also leaves them as that product's bf16 operand
+        h16 = first.group.proj.operand_rows(step)
+        ops.layernorm(x, d, first.norm_w, first.norm_b, c.norm_eps, h, d, T, d, step.st, y16=h16)
         for i, layer in enumerate(self.layers):
-            layer.group.forward(step, h, states[i], y)
+            layer.group.forward(step, h, states[i], y, h16_ready=h16 is not None)
             nxt = self.layers[i + 1] if i + 1 < L else None
             norm_w, norm_b = (nxt.norm_w, nxt.norm_b) if nxt is not None else ((self.final_w, self.final_b) if n_rows else (None, None))
+            h16 = nxt.group.proj.operand_rows(step) if nxt is not None else None
             # the layer's own result, the weighted average over the depth, and the norm of what follows, as one kernel
-            ops.depth_average(x, y, hist, i + 1, layer.depth_coef, norm_w, norm_b, c.norm_eps, h, T, d, step.st)
+            ops.depth_average(x, y, hist, i + 1, layer.depth_coef, norm_w, norm_b, c.norm_eps, h, T, d, step.st, h16=h16)
             if tap is not None:
                 tap(i, x[:T * d].view(T, d))
         if n_rows == 0:

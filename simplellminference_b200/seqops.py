@@ -39,14 +39,18 @@ class Ops:
     def embed(self, ids, table, vocab, d, streams, out, T, st, scale=1.0):
         self._ck(self.lib.sllm_seq_embed(_p(ids), _p(table), self.w_dtype, vocab, d, streams, scale, _p(out), T, st))
 
-    def layernorm(self, x, ldx, w, bias, eps, y, ldy, T, d, st):
-        self._ck(self.lib.sllm_seq_layernorm(_p(x), ldx, _p(w), _p(bias), eps, _p(y), ldy, T, d, st))
+    def layernorm(self, x, ldx, w, bias, eps, y, ldy, T, d, st, y16=None):
+        self._ck(self.lib.sllm_seq_layernorm(_p(x), ldx, _p(w), _p(bias), eps, _p(y), ldy, _p(y16), T, d, st))
 
-    def depth_average(self, x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d, st):
-        self._ck(self.lib.sllm_seq_depth_average(_p(x), _p(y), _p(hist), n_prev, _p(coef), _p(norm_w), _p(norm_b), eps, _p(h), T, d, st))
+    def depth_average(self, x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, T, d, st, h16=None):
+        self._ck(self.lib.sllm_seq_depth_average(_p(x), _p(y), _p(hist), n_prev, _p(coef), _p(norm_w), _p(norm_b), eps, _p(h), _p(h16), T, d, st))
 
-    def clamped_glu(self, gate_ptr, ldg, up_ptr, ldu, limit, alpha, out, ldo, T, n, st):
-        self._ck(self.lib.sllm_seq_clamped_glu(gate_ptr, ldg, up_ptr, ldu, limit, alpha, _p(out), ldo, T, n, st))
+    def clamped_glu(self, gate_ptr, ldg, up_ptr, ldu, limit, alpha, out, ldo, T, n, st, out16=None):
+        self._ck(self.lib.sllm_seq_clamped_glu(gate_ptr, ldg, up_ptr, ldu, limit, alpha, _p(out), ldo, _p(out16), T, n, st))
+
+    def on_tensor_cores(self, T, N, K, ldw=None, batch=1):
+        """Whether ``linear`` with a bf16 scratch sends this product to the tensor cores (then a producer may leave the operand there)."""
+        return bool(self.tensor_cores and self.lib.sllm_seq_linear_on_tensor_cores(T, N, K, self.w_dtype, K if ldw is None else ldw, batch, self.round_a))
 
     def hyper_read(self, x, streams, T, d, coef, norm_w, groups, eps, y, st):
         self._ck(self.lib.sllm_seq_hyper_read(_p(x), streams, T, d, _p(coef), _p(norm_w), groups, eps, _p(y), st))
@@ -58,9 +62,9 @@ class Ops:
         self._ck(self.lib.sllm_seq_hyper_write_read(_p(x), streams, T, d, _p(mix), _p(outc), _p(y_in), _p(coef), _p(norm_w), groups, eps, _p(y_out), st))
 
     def linear(self, a_ptr, lda, w, ldw, bias, c_ptr, ldc, T, N, K, st, alpha=1.0, accumulate=False, batch=1, a_bs=0, w_bs=0, bias_bs=0,
-               c_bs=0, scratch=None):
+               c_bs=0, scratch=None, a16_ready=False):
         self._ck(self.lib.sllm_seq_linear(a_ptr, lda, _p(w), self.w_dtype, ldw, _p(bias), c_ptr, ldc, T, N, K, alpha, int(accumulate),
-                                          self.round_a, batch, a_bs, w_bs, bias_bs, c_bs, _p(scratch) if self.tensor_cores else None, st))
+                                          self.round_a, batch, a_bs, w_bs, bias_bs, c_bs, _p(scratch) if self.tensor_cores else None, int(a16_ready), st))
 
     def polynorm(self, z, ldz, coef, eps, out, ldo, T, n, st):
         self._ck(self.lib.sllm_seq_polynorm(_p(z), ldz, _p(coef), eps, _p(out), ldo, T, n, st))
