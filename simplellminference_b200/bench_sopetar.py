@@ -30,7 +30,7 @@ def sopetar_config(width: int, repeats: int, vocab: int = 32000) -> dict:
            "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "v_mix": True,
                      "mask": {"size": WINDOW, "keep_first": 4}}}
     lat = {"type": "latent_attention", "mlp": mlp,
-           "mixer": {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 128, "scale": 96 ** -0.5, "rot": {"dims": 32, "base": 10000.0},
+           "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 128, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 10000.0},
                      "mask": {"size": WINDOW}}}
     return {"architecture": "Sopetar", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": [att, lat, lat, lat] * repeats}
 

@@ -225,7 +225,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int kMmaDkSteps, int kMmaDvTiles>   // dk <= 16 * kMmaDkSteps (multiple of 16), dv <= 8 * kMmaDvTiles (multiple of 8)
+// kExact: dk = 16 * kMmaDkSteps and dv = 8 * kMmaDvTiles exactly — the loops over fragments then have no run-time bounds, and the compiler
+// is free to interleave independent products (the common head widths are instantiated so).
+template <int kMmaDkSteps, int kMmaDvTiles, bool kExact>   // dk <= 16 * kMmaDkSteps (multiple of 16), dv <= 8 * kMmaDvTiles (multiple of 8)
 __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     extern __shared__ __align__(16) uint16_t smh[];
     const int dk = p.dk, dv = p.dv, ldk = dk + 8, ldvr = p.v_in_k ? ldk : dv + 8;
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     // two warps (16 queries each) per head; a CTA of four warps serves two query heads of the same kv head from one staged tile
     const int hpc = blockDim.x >> 6, h = blockIdx.y * hpc + (warp >> 1), wq = warp & 1;
     const int gkv = h / (p.heads / p.kv_heads);
-    const int dks = dk / 16, dvt = dv / 8;
+    const int dks = kExact ? kMmaDkSteps : dk / 16, dvt = kExact ? kMmaDvTiles : dv / 8;
     const uint16_t* kp = reinterpret_cast<const uint16_t*>(p.k_pool);
     const uint16_t* vp = reinterpret_cast<const uint16_t*>(p.v_pool);
     const int r0 = wq * 16 + g, r1 = r0 + 8;           // this thread's two query rows inside the tile
@@ -362,13 +364,18 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
             split_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3], &ah[3], &al[3]);
             const uint32_t vrow = smem_u32(sV + (ks * 16 + (lane & 15)) * ldvr);   // row-major values: ldmatrix.trans hands out the B fragments
 #pragma unroll
-            for (int nt = 0; nt < kMmaDvTiles; ++nt) {
-                if (nt < dvt) {
-                    uint32_t b0, b1;
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(vrow + nt * 16));
-                    mma_bf16_16816(o[nt], ah, b0, b1);
-                    mma_bf16_16816(o[nt], al, b0, b1);
-                }
+            for (int n0 = 0; n0 < kMmaDvTiles; n0 += 4) {   // four value tiles at a time: no product waits for the one issued just before it
+                uint32_t b0[4], b1[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (n0 + i < kMmaDvTiles && n0 + i < dvt)
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0[i]), "=r"(b1[i]) : "r"(vrow + (n0 + i) * 16));
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (n0 + i < kMmaDvTiles && n0 + i < dvt) mma_bf16_16816(o[n0 + i], ah, b0[i], b1[i]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (n0 + i < kMmaDvTiles && n0 + i < dvt) mma_bf16_16816(o[n0 + i], al, b0[i], b1[i]);
             }
         }
         }
@@ -573,8 +580,13 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
         const size_t smem_mma = 2 * (size_t)kBK * (dk + 8 + (v_in_k ? 0 : dv + 8)) * sizeof(uint16_t);
         const int hpc = (heads / kv_heads) % 2 == 0 ? 2 : 1;   // query heads per CTA
         grid.y = heads / hpc;
-        if (dk <= 128) seq_attention_mma_kernel<8, 16><<<grid, 64 * hpc, smem_mma, as_stream(stream)>>>(p);
-        else seq_attention_mma_kernel<12, 16><<<grid, 64 * hpc, smem_mma, as_stream(stream)>>>(p);
+        const dim3 block(64 * hpc);
+        cudaStream_t st = as_stream(stream);
+        if (dk == 128 && dv == 128) seq_attention_mma_kernel<8, 16, true><<<grid, block, smem_mma, st>>>(p);
+        else if (dk == 192 && dv == 128) seq_attention_mma_kernel<12, 16, true><<<grid, block, smem_mma, st>>>(p);
+        else if (dk == 64 && dv == 64) seq_attention_mma_kernel<4, 8, true><<<grid, block, smem_mma, st>>>(p);
+        else if (dk <= 128) seq_attention_mma_kernel<8, 16, false><<<grid, block, smem_mma, st>>>(p);
+        else seq_attention_mma_kernel<12, 16, false><<<grid, block, smem_mma, st>>>(p);
         ++g_launches;
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;

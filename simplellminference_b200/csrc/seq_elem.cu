@@ -255,6 +255,13 @@ __global__ void seq_clamped_glu_kernel(const float* __restrict__ gate, int ldg, 
     }
 }
 
+// Threads of a one-CTA-per-row kernel: steps of few tokens have few CTAs, and a row walked by 128 threads is a chain of dependent
+// memory latencies (32 of them at 4096 floats); with up to 1024 threads every thread touches the row once or twice.
+static int row_threads(int T, int items, int many_rows_threads) {
+    if (T >= 64) return many_rows_threads;
+    return std::min(1024, std::max(128, (items + 31) / 32 * 32));
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -265,7 +272,7 @@ int sllm_seq_embed(const int32_t* ids, const void* table, int32_t w_dtype, int32
                    int32_t T, sllm_stream_t stream) {
     SLLM_REQUIRE(ids && table && out && T > 0 && d > 0 && vocab > 0 && streams >= 1, SLLM_EINVAL, "seq_embed: bad argument");
     SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_embed: fp32 or bf16 tables");
-    seq_embed_kernel<<<T, 128, 0, as_stream(stream)>>>(ids, table, w_dtype, vocab, d, streams, scale, out, T);
+    seq_embed_kernel<<<T, row_threads(T, d, 128), 0, as_stream(stream)>>>(ids, table, w_dtype, vocab, d, streams, scale, out, T);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
@@ -317,7 +324,7 @@ int sllm_seq_polynorm(const float* z, int32_t ldz, const float* coef, float eps,
 
 int sllm_seq_gather_rows(const float* x, int32_t ldx, const int32_t* rows, int32_t n, int32_t d, float* out, sllm_stream_t stream) {
     SLLM_REQUIRE(x && rows && out && n > 0 && d > 0, SLLM_EINVAL, "seq_gather_rows: bad argument");
-    seq_gather_rows_kernel<<<n, 128, 0, as_stream(stream)>>>(x, ldx, rows, d, out);
+    seq_gather_rows_kernel<<<n, row_threads(n, d, 128), 0, as_stream(stream)>>>(x, ldx, rows, d, out);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
@@ -336,7 +343,7 @@ int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t 
 int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, void* y16, int32_t T,
                        int32_t d, sllm_stream_t stream) {
     SLLM_REQUIRE(x && w && y && T > 0 && d > 0 && ldx >= d && ldy >= d, SLLM_EINVAL, "seq_layernorm: bad argument");
-    seq_layernorm_kernel<<<T, d >= 2048 ? 256 : 128, 0, as_stream(stream)>>>(x, ldx, w, bias, eps, y, ldy, (uint16_t*)y16, d);
+    seq_layernorm_kernel<<<T, row_threads(T, d, d >= 2048 ? 256 : 128), 0, as_stream(stream)>>>(x, ldx, w, bias, eps, y, ldy, (uint16_t*)y16, d);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
@@ -349,7 +356,7 @@ int sllm_seq_depth_average(float* x, const float* y, float* hist, int32_t n_prev
     const size_t smem = (size_t)d * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 4096, SLLM_ENOTSUP, "seq_depth_average: rows of %d floats do not fit shared memory", d);
     const bool vec = d % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)hist % 16) == 0;
-    const int threads = d >= 2048 ? 256 : 128;
+    const int threads = row_threads(T, vec ? d / 4 : d, d >= 2048 ? 256 : 128);
     if (vec) {
         if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_depth_average_kernel<float4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         seq_depth_average_kernel<float4><<<T, threads, smem, as_stream(stream)>>>(x, y, hist, n_prev, coef, norm_w, norm_b, eps, h, (uint16_t*)h16, T, d);

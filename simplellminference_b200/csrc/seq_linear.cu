@@ -1,5 +1,5 @@
 // csrc/seq_linear.cu — sllm_seq_linear: C = alpha * (A . W^T + bias) (+ C) for the ragged token batch. Three bodies:
-//   * rows_kernel  (T <= 8, decode-sized steps): 1 to 8 warps per output column stream that weight row once with 16-byte loads, four in
+//   * rows_kernel  (T <= 8, decode-sized steps): 1 to 8 warps per output column stream that weight row once with 16-byte loads, two batches of two in
 //     flight per lane, one accumulator per activation row — the bandwidth-bound shape of the one-sequence path's GEMV, any size (scalar
 //     loads when unaligned);
 //   * tile_kernel  (any shape): 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMAs with fp32 accumulation. This is
@@ -22,11 +22,18 @@ struct LinArgs {
 };
 
 constexpr int kRowsMax = 8;
+#ifndef SLLM_ROWS_INFLIGHT
+#define SLLM_ROWS_INFLIGHT 2
+#endif
+#ifndef SLLM_ROWS_MINB
+#define SLLM_ROWS_MINB 4   // resident CTAs per SM the register budget is cut for (measured: 4 streams 14 % faster than the unconstrained 3; 5 and more spill)
+#endif
+constexpr int kInFlight = SLLM_ROWS_INFLIGHT;   // 16-byte weight loads per batch and lane; two batches are in flight (measured: 2 x 2 at four resident CTAs beats 1 x 4 by 12 %)
 
 // `wpr` warps (1, 2, 4 or 8) share one output column and cut K among them, so that a matrix with few rows and long rows still fills the
-// machine; a lane keeps four 16-byte weight loads in flight. The partial sums of a column meet in shared memory in a fixed order.
+// machine; a lane keeps two batches of 16-byte weight loads in flight (the next batch travels while this one is multiplied). The partial sums of a column meet in shared memory in a fixed order.
 template <int WD>
-__global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec, int wpr) {
+__global__ void __launch_bounds__(256, SLLM_ROWS_MINB) seq_linear_rows_kernel(LinArgs p, int vec, int wpr) {
     __shared__ float part_sum[8][kRowsMax];
     const int b = blockIdx.y;
     const float* A = p.A + (size_t)b * p.a_bs;
@@ -43,15 +50,17 @@ __global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec
     if (n < p.N) {
         if (vec) {
             const uint8_t* w = reinterpret_cast<const uint8_t*>(p.W) + ((size_t)b * p.w_bs + (size_t)n * p.ldw) * (16 / E);
-            for (int k0 = k_lo + lane * E; k0 < k_hi; k0 += 4 * 32 * E) {
-                uint4 u[4];
+            constexpr int kStep = kInFlight * 32 * E;
+            auto load = [&](uint4 (&u)[kInFlight], int k0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < kInFlight; ++j) {
                     const int k = k0 + j * 32 * E;
                     u[j] = k < k_hi ? ldg_stream(w + (size_t)k * (16 / E)) : make_uint4(0u, 0u, 0u, 0u);
                 }
+            };
+            auto consume = [&](const uint4 (&u)[kInFlight], int k0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < kInFlight; ++j) {
                     const int k = k0 + j * 32 * E;
                     if (k < k_hi) {
                         float wv[E];
@@ -76,6 +85,17 @@ __global__ void __launch_bounds__(256) seq_linear_rows_kernel(LinArgs p, int vec
                         }
                     }
                 }
+            };
+            // two batches of loads: the next one is in flight while the current one is multiplied
+            int k0 = k_lo + lane * E;
+            uint4 cur[kInFlight];
+            load(cur, k0);
+            for (; k0 < k_hi; k0 += kStep) {
+                uint4 nxt[kInFlight];
+                load(nxt, k0 + kStep);
+                consume(cur, k0);
+#pragma unroll
+                for (int j = 0; j < kInFlight; ++j) cur[j] = nxt[j];
             }
         } else {
             for (int k = k_lo + lane; k < k_hi; k += 32) {

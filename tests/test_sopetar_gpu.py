@@ -29,6 +29,11 @@ CFG_ONES = L.make_config([L.attention_layer(heads=1, kv_heads=1, dim=32, vdim=32
 CFG_TC = L.make_config([L.attention_layer(heads=4, kv_heads=2, dim=32, vdim=16, size=40, keep_first=5, v_mix=True, ff=64),
                         L.latent_layer(heads=4, dim=16, rot_dim=16, vdim=24, kv_rank=48, size=40, ff=64),
                         L.attention_layer(heads=4, kv_heads=2, dim=32, vdim=16, size=70, keep_first=2, v_mix=True, ff=64)], width=64)
+# sizes that are multiples of nothing: odd width and vocabulary, head widths that 16-byte loads do not divide, more query heads per
+# key/value head than a decoding work item takes, a window larger than the kept positions' reach and one smaller than them
+CFG_ODD = L.make_config([L.latent_layer(heads=3, dim=6, rot_dim=10, rot_dims=6, vdim=5, kv_rank=13, size=19, keep_first=25, ff=23),
+                         L.attention_layer(heads=34, kv_heads=1, dim=6, vdim=10, size=45, keep_first=50, softcap=3.0, scale=0.7, ff=17),
+                         L.attention_layer(heads=3, kv_heads=3, dim=11, vdim=7, size=2, keep_first=1, v_mix=True, ff=None)], vocab=67, width=50, eps=1e-6)
 
 
 def _engine(tmp_path, cfg, w, dtype="float32", max_tokens=512, max_seqs=4, page_len=32, name="m", **kw):
@@ -264,7 +269,7 @@ def test_feed_forward_alone():
 
 
 # ------------------------------------------------------------------------------------------------ whole models
-@pytest.mark.parametrize("cfg", [CFG_A, CFG_ONES, CFG_TC], ids=["mixed", "ones", "tensorcore"])
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_ONES, CFG_TC, CFG_ODD], ids=["mixed", "ones", "tensorcore", "odd"])
 def test_whole_prompt_matches_oracle_fp32_and_layers(tmp_path, cfg):
     w = L.random_weights(cfg, seed=1)
     toks = np.random.default_rng(2).integers(0, cfg["vocab"], size=140).tolist()
@@ -279,7 +284,7 @@ def test_whole_prompt_matches_oracle_fp32_and_layers(tmp_path, cfg):
     assert L.logit_error(got, want).max() < F32_TOL
 
 
-@pytest.mark.parametrize("cfg", [CFG_A, CFG_TC], ids=["mixed", "tensorcore"])
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_TC, CFG_ODD], ids=["mixed", "tensorcore", "odd"])
 def test_bf16_mode_within_operand_rounding(tmp_path, cfg):
     w = L.random_weights(cfg, seed=3)
     toks = np.random.default_rng(4).integers(0, cfg["vocab"], size=150).tolist()
@@ -295,7 +300,7 @@ def test_bf16_mode_within_operand_rounding(tmp_path, cfg):
         assert e.max() < BF16_TOL and np.median(e) < BF16_TYPICAL, (e.max(), np.median(e))
 
 
-@pytest.mark.parametrize("cfg", [CFG_A, CFG_ONES, CFG_TC], ids=["mixed", "ones", "tensorcore"])
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_ONES, CFG_TC, CFG_ODD], ids=["mixed", "ones", "tensorcore", "odd"])
 def test_prefill_against_token_by_token_and_portions(tmp_path, cfg):
     w = L.random_weights(cfg, seed=5)
     toks = np.random.default_rng(6).integers(0, cfg["vocab"], size=120).tolist()
