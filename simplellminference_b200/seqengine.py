@@ -12,6 +12,9 @@ with prompts processed in chunks beside the decoding requests and the device sam
 Additive to the reference, which decodes one sequence token by token (source/model/model.cpp:148-185)."""
 from __future__ import annotations
 
+import gc
+import weakref
+
 import numpy as np
 import torch
 
@@ -27,7 +30,9 @@ class Step:
     """What the mechanisms see of one step: sizes, the batch description, the stream, scratch memory."""
 
     def __init__(self, engine):
-        self.engine = engine
+        # no strong reference back: an engine must die with its last user (by reference count), not whenever the cycle collector runs —
+        # its captured graphs free device memory when they go, and that is not allowed while another engine is capturing a step
+        self.engine = weakref.proxy(engine)
         self.T = self.nseg = 0
         self.b = _lib.SeqBatch()
         self.st = None
@@ -207,9 +212,15 @@ class SequenceEngine:
             if entry is None:                               # second step of this kind: capture it (a capture does not execute)
                 meta_addr = self._meta_dev.data_ptr()
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    step.st = torch.cuda.current_stream(self.device).cuda_stream
-                    out = self.model.forward(step, ids_t, self.states, rows_t, n_rows)
+                collecting = gc.isenabled()
+                gc.disable()        # a finaliser that frees device memory (another engine's graphs, say) must not run inside the capture
+                try:
+                    with torch.cuda.graph(g):
+                        step.st = torch.cuda.current_stream(self.device).cuda_stream
+                        out = self.model.forward(step, ids_t, self.states, rows_t, n_rows)
+                finally:
+                    if collecting:
+                        gc.enable()
                 entry = self._graphs[key] = (g, out, meta_addr, p[0], p[9])
             g, logits, meta_addr, ids_addr, rows_addr = entry
             if meta_addr != self._meta_dev.data_ptr() or ids_addr != p[0] or rows_addr != p[9]:
