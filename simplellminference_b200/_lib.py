@@ -153,7 +153,7 @@ SIGNATURES.update({
 })
 
 # The ragged-token-batch part of the library can be built and loaded on its own (`make -C csrc seq` -> libsllm_b200_seq.so: the
-# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs seven
+# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs nine
 # translation units compiled, not all of them. The full library contains the same objects and is preferred when it exists.
 SEQ_LIB_PATH = os.path.join(HERE, "lib", "libsllm_b200_seq.so")
 SEQ_SYMBOL_PREFIXES = ("sllm_seq_", "sllm_kvpages_", "sllm_sample_", "sllm_last_error", "sllm_abi_version", "sllm_tune", "sllm_device_info",
